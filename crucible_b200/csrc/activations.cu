@@ -1,6 +1,9 @@
 // Elementwise activations between two products: out = act(z), rows of T with a stride each.
 //   0 squared ReLU: max(z, 0)^2      1 tanh      2 GELU (tanh form)      3 SiLU
 // fp32 arithmetic, rounded once.
+// And the gated pair of a feed-forward, out = gate_act(g) * up(u) over rows [g: F | u: F]:
+//   silu:    g / (1 + exp(-g)) * u
+//   capped:  g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(alpha * g') * (u' + offset)
 #define CB_PDL_BIT 14      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
@@ -27,6 +30,29 @@ __global__ void activation_kernel(const TI* __restrict__ z, int z_stride, TO* __
          i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / width, c = i - t * width;
         out[t * out_stride + c] = cb_from_float<TO>(act_f<KIND>(cb_to_float(z[t * z_stride + c])));
+    }
+}
+
+// limit <= 0: the silu pair; else the capped one.
+__device__ __forceinline__ float glu_f(float g, float u, float limit, float alpha, float offset) {
+    if (limit <= 0.f) return g / (1.0f + expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + offset);
+}
+
+template <typename T>
+__global__ void glu_kernel(const T* __restrict__ both, int both_stride, T* __restrict__ out, int out_stride,
+                           int n_rows, int width, float limit, float alpha, float offset) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const size_t total = (size_t)n_rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width, c = i - t * width;
+        const T* row = both + t * both_stride;
+        out[t * out_stride + c] = cb_from_float<T>(glu_f(cb_to_float(row[c]), cb_to_float(row[width + c]),
+                                                         limit, alpha, offset));
     }
 }
 
@@ -60,4 +86,20 @@ CB_EXPORT int cb_activation(int kind, const void* z, int z_stride, int in_dtype,
     if (out_dtype == CB_F32)
         return launch<__nv_bfloat16, float>(kind, z, z_stride, out, out_stride, n_rows, width, s);
     return launch<__nv_bfloat16, __nv_bfloat16>(kind, z, z_stride, out, out_stride, n_rows, width, s);
+}
+
+// out[T, F] = pair(both[T, 0:F], both[T, F:2F]); limit <= 0: silu(g) * u, else the capped pair.
+CB_EXPORT int cb_glu(const void* both, int both_stride, void* out, int out_stride, int dtype, int n_rows,
+                     int width, float limit, float alpha, float offset, void* stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    const size_t total = (size_t)n_rows * width;
+    const dim3 grid((unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256)), block(256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(glu_kernel<float>, grid, block, 0, s, (const float*)both, both_stride, (float*)out, out_stride,
+                  n_rows, width, limit, alpha, offset);
+    else
+        cb_launch(glu_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)both, both_stride,
+                  (__nv_bfloat16*)out, out_stride, n_rows, width, limit, alpha, offset);
+    return cb_last_error();
 }

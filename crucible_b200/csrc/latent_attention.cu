@@ -12,9 +12,10 @@
 //             head's q_rot into the last `rot` columns of q'.
 //   head gate per (token, head): the head's output times sigmoid(logit).
 //
-// Rotation: of the `rot` features the first `turned` turn (feature i pairs with i + turned/2),
-// the rest pass unchanged; the angle is fp32(position) * freq[i] as an fp32 product, cos and sin
-// (fp32) times `mscale`.
+// Rotation: of the `rot` features the first `turned` turn (split_halves: feature i pairs with
+// i + turned/2; else neighbours 2i, 2i + 1), the rest pass unchanged; the angle is fp32(position)
+// * freq[i] as an fp32 product, cos and sin (fp32) times `mscale`.  A launch may do the pages'
+// part alone (q null) or the queries' part alone (write 0: a layer that reads another layer's rows).
 #define CB_PDL_BIT 15      // this file's bit in CRUCIBLE_PDL
 #include "common.cuh"
 
@@ -30,13 +31,14 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
                                       const int* __restrict__ row_request,
                                       const int* __restrict__ block_table, int table_stride,
                                       T* __restrict__ pages, int n_heads, int dim, int rank, int rot,
-                                      int turned, int page_tokens, int write) {
+                                      int turned, int page_tokens, int write, int split_halves) {
     cb_pdl_trigger();
     cb_pdl_wait();
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = turned >> 1, still = rot - turned;
+    const int step = split_halves ? 1 : 2, apart = split_halves ? half : 1;   // pair j: (j * step, j * step + apart)
     const T* src = dkv + (size_t)t * dkv_stride;
     if (write) {
         const int page = block_table[(size_t)row_request[t] * table_stride + pos / page_tokens];
@@ -53,12 +55,14 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
             float sn, cs;
             sincosf((float)pos * freq[i], &sn, &cs);
             sn *= mscale; cs *= mscale;
-            const float u = cb_to_float(src[rank + i]), v = cb_to_float(src[rank + half + i]);
-            dst[rank + i] = cb_from_float<T>(u * cs - v * sn);
-            dst[rank + half + i] = cb_from_float<T>(v * cs + u * sn);
+            const int ia = rank + i * step, ib = ia + apart;
+            const float u = cb_to_float(src[ia]), v = cb_to_float(src[ib]);
+            dst[ia] = cb_from_float<T>(u * cs - v * sn);
+            dst[ib] = cb_from_float<T>(v * cs + u * sn);
         }
         for (int i = threadIdx.x; i < still; i += blockDim.x) dst[rank + turned + i] = src[rank + turned + i];
     }
+    if (q == nullptr) return;
     for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
         const int h = i / half, j = i - h * half;
         float sn, cs;
@@ -66,9 +70,10 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
         sn *= mscale; cs *= mscale;
         const T* qr = q + (size_t)t * q_stride + (size_t)h * (dim + rot) + dim;
         T* dq = qx + (size_t)t * qx_stride + (size_t)h * (rank + rot) + rank;
-        const float u = cb_to_float(qr[j]), v = cb_to_float(qr[half + j]);
-        dq[j] = cb_from_float<T>(u * cs - v * sn);
-        dq[half + j] = cb_from_float<T>(v * cs + u * sn);
+        const int ia = j * step, ib = ia + apart;
+        const float u = cb_to_float(qr[ia]), v = cb_to_float(qr[ib]);
+        dq[ia] = cb_from_float<T>(u * cs - v * sn);
+        dq[ib] = cb_from_float<T>(v * cs + u * sn);
     }
     for (int i = threadIdx.x; i < n_heads * still; i += blockDim.x) {
         const int h = i / still, j = turned + (i - h * still);
@@ -91,6 +96,20 @@ __global__ void head_gate_kernel(T* __restrict__ x, int x_stride, const float* _
     }
 }
 
+// x[t][i] *= sigmoid(g[t][i]): a gate with a logit of its own for every feature
+template <typename T>
+__global__ void rows_gate_kernel(T* __restrict__ x, int x_stride, const T* __restrict__ g, int g_stride,
+                                 int width) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        T* at = x + (size_t)t * x_stride + i;
+        const float s = 1.0f / (1.0f + expf(-cb_to_float(g[(size_t)t * g_stride + i])));
+        *at = cb_from_float<T>(cb_to_float(*at) * s);
+    }
+}
+
 // Per-head products of a step of few rows: out[t][h][n] = sum_k a[t][h][k] * w[h][n][k].
 // One warp per (head, output feature): its lanes share K, the weight row is read once and meets
 // every row of the step (up to ROWS at a time).  a: rows with a_stride, head h at h * a_head;
@@ -99,8 +118,10 @@ template <typename T, int ROWS>
 __global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride, int a_head,
                                           const T* __restrict__ w, T* __restrict__ out, int out_stride,
                                           int out_head, int n_rows, int n_heads, int N, int K,
-                                          const float* __restrict__ gate_logit, int gate_stride) {
+                                          const float* __restrict__ gate_logit, int gate_stride,
+                                          const T* __restrict__ gate_rows, int gate_rows_stride) {
     // gate_logit (optional): fp32 [rows][heads]; the head's results times sigmoid(logit)
+    // gate_rows (optional): T [rows][heads * N]; every result times the sigmoid of its own logit
     cb_pdl_trigger();
     cb_pdl_wait();
     const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -125,6 +146,8 @@ __global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride,
             if (lane == 0 && t0 + r < n_rows) {
                 if (gate_logit != nullptr)
                     v *= 1.0f / (1.0f + expf(-gate_logit[(size_t)(t0 + r) * gate_stride + h]));
+                if (gate_rows != nullptr)
+                    v *= 1.0f / (1.0f + expf(-cb_to_float(gate_rows[(size_t)(t0 + r) * gate_rows_stride + (size_t)h * N + n])));
                 out[(size_t)(t0 + r) * out_stride + (size_t)h * out_head + n] = cb_from_float<T>(v);
             }
         }
@@ -135,7 +158,8 @@ __global__ void heads_linear_small_kernel(const T* __restrict__ a, int a_stride,
 
 CB_EXPORT int cb_heads_linear_small(const void* a, int a_stride, int a_head, const void* w, void* out,
                                     int out_stride, int out_head, int dtype, int n_rows, int n_heads,
-                                    int N, int K, const float* gate_logit, int gate_stride, void* stream) {
+                                    int N, int K, const float* gate_logit, int gate_stride,
+                                    const void* gate_rows, int gate_rows_stride, void* stream) {
     if (n_rows <= 0 || n_heads <= 0 || N <= 0) return 0;
     const int warps = 4;
     const dim3 grid((unsigned)(((long)n_heads * N + warps - 1) / warps)), block(warps * 32);
@@ -143,11 +167,11 @@ CB_EXPORT int cb_heads_linear_small(const void* a, int a_stride, int a_head, con
     if (dtype == CB_F32)
         cb_launch(heads_linear_small_kernel<float, 8>, grid, block, 0, s, (const float*)a, a_stride, a_head,
                   (const float*)w, (float*)out, out_stride, out_head, n_rows, n_heads, N, K, gate_logit,
-                  gate_stride);
+                  gate_stride, (const float*)gate_rows, gate_rows_stride);
     else
         cb_launch(heads_linear_small_kernel<__nv_bfloat16, 8>, grid, block, 0, s, (const __nv_bfloat16*)a,
                   a_stride, a_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, out_head, n_rows,
-                  n_heads, N, K, gate_logit, gate_stride);
+                  n_heads, N, K, gate_logit, gate_stride, (const __nv_bfloat16*)gate_rows, gate_rows_stride);
     return cb_last_error();
 }
 
@@ -156,21 +180,35 @@ CB_EXPORT int cb_latent_prepare(const void* dkv, int dkv_stride, const void* q, 
                                 float mscale, float eps, const int* positions, const int* row_request,
                                 const int* block_table, int table_stride, void* pages, int n_rows,
                                 int n_heads, int dim, int rank, int rot, int turned, int page_tokens,
-                                int write, void* stream) {
+                                int write, int split_halves, void* stream) {
     if (n_rows <= 0) return 0;
     if (rot < 0 || turned < 0 || turned > rot || (turned & 1) || rank <= 0) return CB_ERR_UNSUPPORTED;
+    if ((write && dkv == nullptr) || (!write && q == nullptr)) return CB_ERR_UNSUPPORTED;
     const dim3 grid(n_rows), block(rank >= 512 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
         cb_launch(latent_prepare_kernel<float>, grid, block, 0, s, (const float*)dkv, dkv_stride,
                   (const float*)q, q_stride, (float*)qx, qx_stride, gain, freq, mscale, eps, positions,
                   row_request, block_table, table_stride, (float*)pages, n_heads, dim, rank, rot,
-                  turned, page_tokens, write);
+                  turned, page_tokens, write, split_halves);
     else
         cb_launch(latent_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)dkv,
                   dkv_stride, (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)qx, qx_stride, gain, freq,
                   mscale, eps, positions, row_request, block_table, table_stride, (__nv_bfloat16*)pages,
-                  n_heads, dim, rank, rot, turned, page_tokens, write);
+                  n_heads, dim, rank, rot, turned, page_tokens, write, split_halves);
+    return cb_last_error();
+}
+
+CB_EXPORT int cb_rows_gate(void* x, int x_stride, const void* g, int g_stride, int dtype, int n_rows,
+                           int width, void* stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    const dim3 grid(n_rows), block(width >= 1024 ? 256 : 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(rows_gate_kernel<float>, grid, block, 0, s, (float*)x, x_stride, (const float*)g, g_stride, width);
+    else
+        cb_launch(rows_gate_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)x, x_stride,
+                  (const __nv_bfloat16*)g, g_stride, width);
     return cb_last_error();
 }
 

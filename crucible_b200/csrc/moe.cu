@@ -8,7 +8,7 @@
 //            pair's place among its expert's pairs (a counter per expert)
 //   plan     one block: where each expert's pairs start in the sorted order, the list of
 //            row tiles (an expert, a start, a count), and the sorted order itself
-//   tiles    gate/up with SiLU, then down times the pair's weight: a block owns a tile of
+//   tiles    gate/up with the gated pair (SiLU, or the capped form), then down times the pair's weight: a block owns a tile of
 //            rows of one expert and a tile of columns; rows beyond the tile's count and
 //            tiles beyond the plan's count do nothing.  fp32 sums over ascending k, so a
 //            pair's result does not depend on which other pairs share its tile.
@@ -21,9 +21,18 @@ namespace {
 constexpr int TM = 32, TN = 64, TK = 32, THREADS = 128;
 constexpr int MAX_PER_LANE = 8;       // experts <= 256, of which a token takes at most 32
 
-__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+// The gated pair of an expert.  limit <= 0: silu(g) * u.  Else the capped pair:
+// g' = min(g, limit), u' = clamp(u, -limit, limit): g' * sigmoid(alpha * g') * (u' + offset).
+struct GateRule { float limit, alpha, offset; };
+__device__ __forceinline__ float gated_f(float g, float u, const GateRule& p) {
+    if (p.limit <= 0.f) return g / (1.0f + expf(-g)) * u;
+    g = fminf(g, p.limit);
+    u = fminf(fmaxf(u, -p.limit), p.limit);
+    return g / (1.0f + expf(-p.alpha * g)) * (u + p.offset);
+}
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
+__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                 int n_tokens, int E, int top,
                                  int* __restrict__ idx, float* __restrict__ weight,
                                  int* __restrict__ place, int* __restrict__ count) {
     cb_pdl_trigger();
@@ -35,7 +44,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens,
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        v[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
+        v[i] = e < E ? logits[(size_t)t * E + e] + (bias != nullptr ? bias[e] : 0.f) : -INFINITY;
     }
     float first = 0.f, total = 0.f, mine = 0.f;
     int mine_e = 0;
@@ -108,7 +117,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(THREADS) moe_tile_kernel(
     const T* __restrict__ a, int a_stride, const T* __restrict__ w, long expert_stride, int N, int K,
     const int* __restrict__ plan, int E, int max_tiles, const int* __restrict__ sorted_pair, int top,
-    const float* __restrict__ weight, void* __restrict__ out_, int out_stride) {
+    const float* __restrict__ weight, void* __restrict__ out_, int out_stride, GateRule rule) {
     cb_pdl_trigger();
     cb_pdl_wait();
     const int tile = blockIdx.x;
@@ -166,7 +175,7 @@ __global__ void __launch_bounds__(THREADS) moe_tile_kernel(
             T* dst = reinterpret_cast<T*>(out_) + (size_t)s * out_stride;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                if (n0 + tc + j < N) dst[n0 + tc + j] = cb_from_float<T>(silu_f(acc[0][i][j]) * acc[GATED ? 1 : 0][i][j]);
+                if (n0 + tc + j < N) dst[n0 + tc + j] = cb_from_float<T>(gated_f(acc[0][i][j], acc[GATED ? 1 : 0][i][j], rule));
         } else {
             const int p = sorted_pair[s];
             const float wt = weight[p];
@@ -215,7 +224,7 @@ template <typename T, bool GATED, int ROWS>
 __global__ void __launch_bounds__(256, 3) moe_rows_small_kernel(
     const T* __restrict__ a, int a_stride, const T* __restrict__ w, long expert_stride, int N, int K,
     const int* __restrict__ plan, int E, int max_tiles, const int* __restrict__ sorted_pair, int top,
-    const float* __restrict__ weight, void* __restrict__ out_, int out_stride, int per_block) {
+    const float* __restrict__ weight, void* __restrict__ out_, int out_stride, int per_block, GateRule rule) {
     cb_pdl_trigger();
     cb_pdl_wait();
     const int tile = blockIdx.x;
@@ -280,7 +289,7 @@ __global__ void __launch_bounds__(256, 3) moe_rows_small_kernel(
                 if (lane == 0) {
                     const int s = start + r0 + r;
                     if (GATED) {
-                        reinterpret_cast<T*>(out_)[(size_t)s * out_stride + n] = cb_from_float<T>(silu_f(g) * u);
+                        reinterpret_cast<T*>(out_)[(size_t)s * out_stride + n] = cb_from_float<T>(gated_f(g, u, rule));
                     } else {
                         const int p = sorted_pair[s];
                         reinterpret_cast<float*>(out_)[(size_t)p * out_stride + n] = weight[p] * g;
@@ -329,13 +338,14 @@ __global__ void moe_scatter_kernel(const float* __restrict__ rows, const int* __
 
 CB_EXPORT int cb_moe_tile_rows() { return TM; }
 
-CB_EXPORT int cb_moe_route(const float* logits, int n_tokens, int E, int top, int* idx, float* weight,
+CB_EXPORT int cb_moe_route(const float* logits, const float* bias, int n_tokens, int E, int top, int* idx,
+                           float* weight,
                            int* place, int* count, int* plan, int max_tiles, int* sorted_pair,
                            void* stream) {
     if (n_tokens <= 0) return 0;
     if (E > 32 * MAX_PER_LANE || top > E || top <= 0 || top > 32) return CB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    cb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, s, logits, n_tokens, E, top, idx,
+    cb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, s, logits, bias, n_tokens, E, top, idx,
               weight, place, count);
     cb_launch(moe_plan_kernel, dim3(1), dim3(256), 0, s, count, E, n_tokens * top, (const int*)idx,
               (const int*)place, plan, max_tiles, sorted_pair);
@@ -346,13 +356,14 @@ CB_EXPORT int cb_moe_route(const float* logits, int n_tokens, int E, int top, in
 CB_EXPORT int cb_moe_tiles(int gated, const void* a, int a_stride, const void* w, long expert_stride,
                            int dtype, int N, int K, const int* plan, int E, int max_tiles,
                            const int* sorted_pair, int top, const float* weight, void* out,
-                           int out_stride, void* stream) {
+                           int out_stride, float limit, float alpha, float offset, void* stream) {
     if (max_tiles <= 0) return 0;
+    const GateRule rule = {limit, alpha, offset};
     const dim3 grid(max_tiles, (N + TN - 1) / TN), block(THREADS);
     cudaStream_t s = (cudaStream_t)stream;
 #define CB_MOE(TT, GG)                                                                             \
     cb_launch(moe_tile_kernel<TT, GG>, grid, block, 0, s, (const TT*)a, a_stride, (const TT*)w,    \
-              expert_stride, N, K, plan, E, max_tiles, sorted_pair, top, weight, out, out_stride)
+              expert_stride, N, K, plan, E, max_tiles, sorted_pair, top, weight, out, out_stride, rule)
     if (dtype == CB_F32) { if (gated) CB_MOE(float, true); else CB_MOE(float, false); }
     else { if (gated) CB_MOE(__nv_bfloat16, true); else CB_MOE(__nv_bfloat16, false); }
 #undef CB_MOE
@@ -363,8 +374,9 @@ CB_EXPORT int cb_moe_tiles(int gated, const void* a, int a_stride, const void* w
 CB_EXPORT int cb_moe_rows_small(int gated, const void* a, int a_stride, const void* w, long expert_stride,
                                 int dtype, int N, int K, const int* plan, int E, int max_tiles,
                                 const int* sorted_pair, int top, const float* weight, void* out,
-                                int out_stride, void* stream) {
+                                int out_stride, float limit, float alpha, float offset, void* stream) {
     if (max_tiles <= 0) return 0;
+    const GateRule rule = {limit, alpha, offset};
     if (K % 8 || a_stride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return CB_ERR_UNSUPPORTED;
     // enough blocks to keep the memory busy: about four to an SM over all tiles
     int chunks = (4 * 148 + max_tiles - 1) / max_tiles;
@@ -387,7 +399,7 @@ CB_EXPORT int cb_moe_rows_small(int gated, const void* a, int a_stride, const vo
         }                                                                                               \
         cb_launch(moe_rows_small_kernel<TT, GG, 4>, grid, block, smem, s, (const TT*)a, a_stride,       \
                   (const TT*)w, expert_stride, N, K, plan, E, max_tiles, sorted_pair, top, weight, out, \
-                  out_stride, per_block);                                                               \
+                  out_stride, per_block, rule);                                                         \
     } while (0)
     if (dtype == CB_F32) { if (gated) CB_MOE(float, true); else CB_MOE(float, false); }
     else { if (gated) CB_MOE(__nv_bfloat16, true); else CB_MOE(__nv_bfloat16, false); }

@@ -1,5 +1,7 @@
 // Paged softmax attention whose window keeps the first tokens and whose denominator
-// holds a learned sink.  Two kernels.
+// may hold a learned sink.  Two kernels (the preparation in two forms: the one described
+// first, and a general one with an RMS norm of q and k, either pairing of the rotation and
+// values cached as they are).
 //
 // (1) Preparation of a step's rows, one block per token.  A row of the joint
 //     projection is [q: H*D | k: G*D | v: G*E | ...].  Pairs (2i, 2i+1), i < R/2, of
@@ -79,6 +81,88 @@ __global__ void rotate_norm_append_kernel(T* __restrict__ proj, int proj_stride,
         const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)value_dim + value_eps);
         T* dst = v_cache + v_base + (size_t)h * v_head_stride;
         for (int e = lane; e < value_dim; e += 32) dst[e] = cb_from_float<T>(cb_to_float(v[e]) * r);
+    }
+}
+
+// The general preparation: a warp per head of the token's row [q: H*D | k: G*D | v: G*E].
+// Every q and k head may first be divided by its root mean square over D (eps under the root)
+// and multiplied by a gain over D that all heads share (q_gain / k_gain null: no norm); then
+// the first R features turn, as neighbouring pairs (2i, 2i + 1) or as split halves (i, i + R/2),
+// by the fp32 angle position * freq[i]; q stays in the row, k goes to the pages.  Values are
+// divided by their root mean square when value_eps >= 0 and copied as they are otherwise.
+// Norms, angles and the rotation are fp32; one rounding to T at the end.
+template <typename T>
+__global__ void norm_rotate_append_kernel(T* __restrict__ proj, int proj_stride,
+                                          const float* __restrict__ q_gain,
+                                          const float* __restrict__ k_gain, float qk_eps,
+                                          const float* __restrict__ freq, int rotary_dim, int split_halves,
+                                          const int* __restrict__ positions,
+                                          const int* __restrict__ row_request,
+                                          const int* __restrict__ block_table, int table_stride,
+                                          T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          int n_heads, int n_kv_heads, int key_dim, int value_dim,
+                                          int page_tokens, int write_cache, float value_eps) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    extern __shared__ float head_rows[];          // a row of key_dim floats per warp
+    const int t = blockIdx.x;
+    T* row = proj + (size_t)t * proj_stride;
+    const int pos = positions[t];
+    const int half = rotary_dim >> 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    size_t k_base = 0, v_base = 0;
+    const size_t k_head_stride = (size_t)page_tokens * key_dim;
+    const size_t v_head_stride = (size_t)page_tokens * value_dim;
+    if (write_cache) {
+        const int page = block_table[(size_t)row_request[t] * table_stride + pos / page_tokens];
+        k_base = (size_t)page * n_kv_heads * k_head_stride + (size_t)(pos % page_tokens) * key_dim;
+        v_base = (size_t)page * n_kv_heads * v_head_stride + (size_t)(pos % page_tokens) * value_dim;
+    }
+    float* mine = head_rows + (size_t)warp * key_dim;
+    const int n_turn_heads = n_heads + (write_cache ? n_kv_heads : 0);
+    for (int h = warp; h < n_turn_heads; h += n_warps) {
+        const bool is_q = h < n_heads;
+        T* src = row + (size_t)h * key_dim;
+        const float* gain = is_q ? q_gain : k_gain;
+        float ss = 0.f;
+        for (int f = lane; f < key_dim; f += 32) {
+            const float x = cb_to_float(src[f]);
+            mine[f] = x;
+            ss = fmaf(x, x, ss);
+        }
+        if (gain != nullptr) {
+            const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)key_dim + qk_eps);
+            for (int f = lane; f < key_dim; f += 32) mine[f] = mine[f] * r * gain[f];
+        }
+        __syncwarp();
+        T* dst = is_q ? src : k_cache + k_base + (size_t)(h - n_heads) * k_head_stride;
+        for (int j = lane; j < half; j += 32) {
+            const int ia = split_halves ? j : 2 * j, ib = split_halves ? j + half : 2 * j + 1;
+            float s, c;
+            sincosf((float)pos * freq[j], &s, &c);
+            const float a = mine[ia], b = mine[ib];
+            dst[ia] = cb_from_float<T>(a * c - b * s);
+            dst[ib] = cb_from_float<T>(b * c + a * s);
+        }
+        for (int f = rotary_dim + lane; f < key_dim; f += 32) dst[f] = cb_from_float<T>(mine[f]);
+        __syncwarp();
+    }
+    if (!write_cache) return;
+    const T* v_src = row + (size_t)(n_heads + n_kv_heads) * key_dim;
+    for (int h = warp; h < n_kv_heads; h += n_warps) {
+        const T* v = v_src + (size_t)h * value_dim;
+        T* dst = v_cache + v_base + (size_t)h * v_head_stride;
+        if (value_eps >= 0.f) {
+            float ss = 0.f;
+            for (int e = lane; e < value_dim; e += 32) {
+                const float x = cb_to_float(v[e]);
+                ss = fmaf(x, x, ss);
+            }
+            const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)value_dim + value_eps);
+            for (int e = lane; e < value_dim; e += 32) dst[e] = cb_from_float<T>(cb_to_float(v[e]) * r);
+        } else {
+            for (int e = lane; e < value_dim; e += 32) dst[e] = v[e];
+        }
     }
 }
 
@@ -182,6 +266,37 @@ CB_EXPORT int cb_rotate_norm_append(void* proj, int proj_stride, int dtype, cons
                   (__nv_bfloat16*)proj, proj_stride, freq, rotary_dim, positions, row_request,
                   block_table, table_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads,
                   n_kv_heads, key_dim, value_dim, page_tokens, write_cache, value_eps);
+    return cb_last_error();
+}
+
+// The general preparation (see norm_rotate_append_kernel): q_gain / k_gain null: no norm of
+// q and k; split_halves 0: neighbouring pairs turn, 1: feature i with i + rotary_dim / 2;
+// value_eps < 0: values are cached as they are.
+CB_EXPORT int cb_norm_rotate_append(void* proj, int proj_stride, int dtype, const float* q_gain,
+                                    const float* k_gain, float qk_eps, const float* freq,
+                                    int rotary_dim, int split_halves, const int* positions,
+                                    const int* row_request, const int* block_table, int table_stride,
+                                    void* k_cache, void* v_cache, int n_rows, int n_heads,
+                                    int n_kv_heads, int key_dim, int value_dim, int page_tokens,
+                                    int write_cache, float value_eps, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > key_dim || (rotary_dim & 1) || key_dim > 4096) return CB_ERR_UNSUPPORTED;
+    int warps = n_heads + n_kv_heads;
+    warps = warps > 8 ? 8 : warps;
+    const size_t smem = (size_t)warps * key_dim * sizeof(float);
+    if (smem > 48 * 1024) return CB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(norm_rotate_append_kernel<float>, dim3(n_rows), dim3(warps * 32), smem, s, (float*)proj,
+                  proj_stride, q_gain, k_gain, qk_eps, freq, rotary_dim, split_halves, positions,
+                  row_request, block_table, table_stride, (float*)k_cache, (float*)v_cache, n_heads,
+                  n_kv_heads, key_dim, value_dim, page_tokens, write_cache, value_eps);
+    else
+        cb_launch(norm_rotate_append_kernel<__nv_bfloat16>, dim3(n_rows), dim3(warps * 32), smem, s,
+                  (__nv_bfloat16*)proj, proj_stride, q_gain, k_gain, qk_eps, freq, rotary_dim,
+                  split_halves, positions, row_request, block_table, table_stride,
+                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, key_dim,
+                  value_dim, page_tokens, write_cache, value_eps);
     return cb_last_error();
 }
 

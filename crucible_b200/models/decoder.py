@@ -62,9 +62,11 @@ class DecoderModel:
         """Cache groups, one binding per run-order entry, state bytes per request."""
         owners: Dict[int, Tuple[int, int]] = {}       # stored layer -> (group, slot)
         groups: List[Tuple[CacheNeed, List[int]]] = []
+        # a layer that only ever runs on another layer's cache gets no pages of its own
+        runs_on_own = {e.layer for e in self.config.run_order if e.cache_of is None}
         for li, layer in enumerate(self.layers):
             need = layer.mixer.cache_need()
-            if need is None:
+            if need is None or li not in runs_on_own:
                 continue
             for gi, (gneed, members) in enumerate(groups):
                 if gneed == need:

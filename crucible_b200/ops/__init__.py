@@ -172,6 +172,24 @@ def activation(kind: str, z: torch.Tensor, out: torch.Tensor) -> None:
                              _c_int(z.shape[0]), _c_int(z.shape[1]), _stream()), f"activation {kind}")
 
 
+def glu(both: torch.Tensor, out: torch.Tensor, limit: Optional[float] = None, alpha: float = 1.0,
+        offset: float = 0.0) -> None:
+    """out[T, F] from rows [g: F | u: F].  `limit` None: silu(g) * u.  A number: the capped pair,
+    g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' * sigmoid(alpha * g') * (u' + offset).
+    float32 arithmetic, rounded once."""
+    _need_cuda(both, out)
+    if (both.dtype != out.dtype or both.dim() != 2 or both.shape != (out.shape[0], 2 * out.shape[1])
+            or both.stride(1) != 1 or out.stride(1) != 1):
+        raise KernelError("glu takes rows [T, 2F] and writes [T, F] of the same dtype")
+    if limit is not None and not limit > 0:
+        raise KernelError("glu: the limit must be positive")
+    lib = build.load("activations")
+    _check(lib.cb_glu(_ptr(both), _c_int(both.stride(0)), _ptr(out), _c_int(out.stride(0)),
+                      _c_int(_code(out.dtype)), _c_int(out.shape[0]), _c_int(out.shape[1]),
+                      _c_float(limit if limit is not None else 0.0), _c_float(alpha), _c_float(offset),
+                      _stream()), "glu")
+
+
 def hashed_embedding(table, bigram, positions_table, ids, ctx, state, out, scale: float, buckets: int,
                      mul_prev: int, mul_cur: int, device_tokens=None) -> None:
     """out[t] = table[id] * scale + bigram[hash(previous id, id)] + positions_table[position];

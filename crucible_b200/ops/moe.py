@@ -22,25 +22,35 @@ def plan_ints(n_experts: int, tiles: int) -> int:
     return 2 + n_experts + 3 * tiles
 
 
-def route(logits, top: int, idx, weight, place, count, plan, tiles: int, sorted_pair) -> None:
-    """Per token the `top` largest logits (the lower index on ties) and their softmax; then
+def _pair(pair):
+    """(limit, alpha, offset) of the capped gated pair as C floats; None: silu(g) * u."""
+    limit, alpha, offset = pair if pair is not None else (0.0, 1.0, 0.0)
+    return ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(offset)
+
+
+def route(logits, top: int, idx, weight, place, count, plan, tiles: int, sorted_pair, bias=None) -> None:
+    """Per token the `top` largest logits (plus `bias`, float32 [experts], if given; the lower
+    index on ties) and their softmax; then
     the sorted order of the (token, choice) pairs by expert and the tiles over it.  `count`
     (int32 [experts]) is zero between calls: the kernels leave it so."""
-    _need_cuda(logits, idx, weight, place, count, plan, sorted_pair)
+    _need_cuda(logits, idx, weight, place, count, plan, sorted_pair, bias)
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise KernelError("moe route takes contiguous float32 logits [tokens, experts]")
     t, e = logits.shape
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != e or not bias.is_contiguous()):
+        raise KernelError("moe route: the bias is float32 [experts]")
     if idx.numel() < t * top or plan.numel() < plan_ints(e, tiles) or sorted_pair.numel() < t * top:
         raise KernelError("moe route: a buffer is too small")
     lib = build.load("moe")
-    _check(lib.cb_moe_route(_ptr(logits), _c_int(t), _c_int(e), _c_int(top), _ptr(idx), _ptr(weight),
+    _check(lib.cb_moe_route(_ptr(logits), _ptr(bias), _c_int(t), _c_int(e), _c_int(top), _ptr(idx), _ptr(weight),
                             _ptr(place), _ptr(count), _ptr(plan), _c_int(tiles), _ptr(sorted_pair),
                             _stream()), "moe route")
 
 
 def expert_tiles(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles: int, sorted_pair, top: int,
-                 weight, out) -> None:
-    """gated: out[sorted place] = silu(a[token] Wg^T) * (a[token] Wu^T) with w [experts, 2 n_out, K];
+                 weight, out, pair=None) -> None:
+    """gated: out[sorted place] = silu(a[token] Wg^T) * (a[token] Wu^T) with w [experts, 2 n_out, K]
+    (`pair` = (limit, alpha, offset): the capped pair instead, see `ops.glu`);
     else: out[pair] = weight[pair] * a[sorted place] Wd^T with w [experts, n_out, K], float32."""
     _need_cuda(a, w, plan, sorted_pair, weight, out)
     if a.dtype != w.dtype or a.stride(1) != 1 or not w.is_contiguous() or out.stride(1) != 1:
@@ -52,12 +62,12 @@ def expert_tiles(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles: int
                             ctypes.c_long(w.stride(0)), _c_int(_code(a.dtype)), _c_int(n_out),
                             _c_int(w.shape[2]), _ptr(plan), _c_int(n_experts), _c_int(tiles),
                             _ptr(sorted_pair), _c_int(top), _ptr(weight), _ptr(out),
-                            _c_int(out.stride(0)), _stream()),
+                            _c_int(out.stride(0)), *_pair(pair), _stream()),
            "moe gate/up" if gated else "moe down")
 
 
 def expert_rows_small(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles: int, sorted_pair,
-                      top: int, weight, out) -> bool:
+                      top: int, weight, out, pair=None) -> bool:
     """`expert_tiles` for steps of few rows: every weight row is read once by one warp.  False:
     the sizes do not allow it (K not a multiple of 8, rows not 16-byte aligned)."""
     _need_cuda(a, w, plan, sorted_pair, weight, out)
@@ -68,7 +78,7 @@ def expert_rows_small(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles
                                  ctypes.c_long(w.stride(0)), _c_int(_code(a.dtype)), _c_int(n_out),
                                  _c_int(w.shape[2]), _ptr(plan), _c_int(n_experts), _c_int(tiles),
                                  _ptr(sorted_pair), _c_int(top), _ptr(weight), _ptr(out),
-                                 _c_int(out.stride(0)), _stream())
+                                 _c_int(out.stride(0)), *_pair(pair), _stream())
     if code == 100001:
         return False
     _check(code, "moe gate/up (few rows)" if gated else "moe down (few rows)")

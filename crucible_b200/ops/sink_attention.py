@@ -34,6 +34,40 @@ def rotate_norm_append(proj: torch.Tensor, freq: Optional[torch.Tensor], rotary_
         _c_int(1 if binding.write else 0), _c_float(value_eps), _stream()), "rotate_norm_append")
 
 
+def norm_rotate_append(proj: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
+                       qk_eps: float, freq: Optional[torch.Tensor], rotary_dim: int, split_halves: bool,
+                       n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int,
+                       value_eps: Optional[float], ctx, cache, binding) -> None:
+    """The general preparation of rows [q | k | v | ...]: every q and k head is divided by its
+    root mean square and multiplied by `q_gain` / `k_gain` (float32 [key_dim], shared by the
+    heads; None: no norm), then its first `rotary_dim` features turn by position * freq, as
+    neighbouring pairs or as split halves; q in place, k and v to the token's place in the
+    pages; v divided by its root mean square if `value_eps` is given."""
+    _need_cuda(proj, q_gain, k_gain, freq)
+    if proj.stride(1) != 1:
+        raise KernelError("norm_rotate_append: rows must be contiguous")
+    if rotary_dim and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rotary_dim):
+        raise KernelError("norm_rotate_append: freq is float32 [rotary_dim / 2]")
+    for g in (q_gain, k_gain):
+        if g is not None and (g.dtype != torch.float32 or g.numel() != key_dim or not g.is_contiguous()):
+            raise KernelError("norm_rotate_append: a gain is float32 [key_dim]")
+    k_cache, v_cache = cache.keys(binding.slot), cache.values(binding.slot)
+    if k_cache.dtype != proj.dtype:
+        raise KernelError("norm_rotate_append: cache dtype differs from the activations'")
+    if k_cache.shape[-1] != key_dim or v_cache.shape[-1] != value_dim:
+        raise KernelError("norm_rotate_append: the pages' sizes differ from the heads'")
+    table = ctx.block_table(binding.group)
+    lib = build.load("sink_attention")
+    _check(lib.cb_norm_rotate_append(
+        _ptr(proj), _c_int(proj.stride(0)), _c_int(_code(proj.dtype)), _ptr(q_gain), _ptr(k_gain),
+        _c_float(qk_eps), _ptr(freq), _c_int(rotary_dim), _c_int(1 if split_halves else 0),
+        _ptr(ctx.positions), _ptr(ctx.row_request), _ptr(table), _c_int(table.shape[1]),
+        _ptr(k_cache), _ptr(v_cache), _c_int(proj.shape[0]), _c_int(n_heads), _c_int(n_kv_heads),
+        _c_int(key_dim), _c_int(value_dim), _c_int(cache.page_tokens),
+        _c_int(1 if binding.write else 0), _c_float(-1.0 if value_eps is None else value_eps), _stream()),
+        "norm_rotate_append")
+
+
 def attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
               sinks: Optional[torch.Tensor], n_heads: int, n_kv_heads: int, key_dim: int,
               value_dim: int, scale: float, window: Optional[int], keep_first: int,

@@ -1,6 +1,7 @@
 """Block arrangements.  `pre_norm` is the only one the reference runs on the
 GPU (`model.py:262-264`, `engine/src/gpu_model.rs:518-520`):
-x = x + mixer(norm(x)); x = x + ffn(norm(x))."""
+x = x + mixer(norm(x)); x = x + ffn(norm(x)).  `parallel` has one norm that both
+sublayers read: with n = norm(x), x = x + mixer(n) + ffn(n)."""
 from __future__ import annotations
 
 from .base import ARRANGEMENTS, Arrangement
@@ -58,4 +59,25 @@ class PreNormBlock(Arrangement):
         return norm.forward(ctx, x)
 
 
+class ParallelBlock(Arrangement):
+    """One norm, two readers: n = norm(x); x += mixer(n); x += ffn(n).  Both sublayers add
+    their results into the fp32 residual, so the layer's sum is a 32-bit sum; the order of
+    the two additions is fixed.  A feed-forward part with `absent` leaves the mixer alone."""
+    norm_names = ("norm",)
+
+    def __init__(self, spec, norms, mixer, feed_forward):
+        self.has_ffn = not getattr(feed_forward, "absent", False)
+        super().__init__(spec, norms, mixer, feed_forward)
+
+    def forward(self, ctx, x, binding):
+        announce = getattr(ctx, "announce_norm", None)
+        if announce is not None:
+            announce(None, None)       # the rows' next norm reads them after BOTH sublayers
+        n = self.norms["norm"].forward(ctx, x)
+        self.mixer.forward(ctx, n, x, binding)
+        if self.has_ffn:
+            self.feed_forward.forward(ctx, n, x)
+
+
 ARRANGEMENTS.register("pre_norm", PreNormBlock)
+ARRANGEMENTS.register("parallel", ParallelBlock)

@@ -36,21 +36,27 @@ class TokenEmbedding(Embedding):
 
 class NormedStreamsEmbedding(Embedding):
     """x0 = rmsnorm(table[token]) * gain, copied into every one of `streams` residual
-    streams: fp32 [T, streams, width] (or [T, width] when `streams` is None)."""
+    streams: fp32 [T, streams, width] (or [T, width] when `streams` is None).  Option
+    `gain_offset`: the stored weight plus this number is the gain (a weight kept around zero)."""
 
     def __init__(self, spec, vocab_size: int, width: int):
         self.vocab_size = vocab_size
         self.width = width
         self.eps = float(spec.option("eps", 1e-6))
         self.streams = spec.option("streams")
+        # the norm's weight may be stored around zero: the gain is then 1 + weight
+        self.gain_offset = float(spec.option("gain_offset", 0.0))
         self.table = self.gain = None
 
     def tensors(self):
+        init = ("normal", 0.0, 0.1) if self.gain_offset else None
         return [TensorDecl("table", (self.vocab_size, self.width)),
-                TensorDecl("norm_gain", (self.width,), role="vector")]
+                TensorDecl("norm_gain", (self.width,), role="vector", init=init)]
 
     def bind(self, tensors, dtype, device):
         self.table, self.gain = tensors["table"], tensors["norm_gain"]
+        if self.gain_offset:
+            self.gain = (self.gain.to(torch.float32) + self.gain_offset).contiguous()
         ops.declare_weights(self.table)
 
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:

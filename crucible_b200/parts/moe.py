@@ -4,10 +4,16 @@ experts.
 `dense_act`: x += act(h Wup^T) Wdown^T; the activation is an option of the spec (relu2:
 the square of ReLU; gelu_tanh; silu; tanh).
 
+`glu_capped`: x += pair(h Wg^T, h Wu^T) Wdown^T with the capped gated pair: g' = min(g, limit),
+u' = clamp(u, -limit, limit), pair = g' * sigmoid(alpha * g') * (u' + offset); `limit`, `alpha`
+(default 1.702) and `offset` (default 1) are options of the spec.
+
 `moe`: `experts` gated feed-forwards Wd_e (silu(Wg_e h) * (Wu_e h)) without biases, of
 which a token uses the `top` with the largest router logits z = h Wr^T (float32; the lower
 index on ties), weighted by the softmax over those `top` logits alone; an optional shared
-expert of the same form runs for every token and is added.
+expert of the same form runs for every token and is added.  Options: `router_bias` (the
+logits are h Wr^T + b, tensor `router.b`), `pair` = (limit, alpha, offset): the experts use
+the capped gated pair instead of silu(g) * u.
 """
 from __future__ import annotations
 
@@ -47,6 +53,38 @@ class ActivatedFeedForward(FeedForward):
         ops.linear(z, self.down, residual, accumulate=True, closes=ctx)
 
 
+class CappedGLU(FeedForward):
+    fuses_norm = True
+    takes_prenormed = False
+
+    def __init__(self, spec: FeedForwardSpec):
+        self.spec = spec
+        self.limit = float(spec.option("limit", 0.0))
+        self.alpha = float(spec.option("alpha", 1.702))
+        self.offset = float(spec.option("offset", 1.0))
+        if not self.limit > 0:
+            raise ValueError("glu_capped: the limit must be positive")
+        self.gate_up = self.down = None
+
+    def tensors(self):
+        d, f = self.spec.width, self.spec.intermediate
+        return [TensorDecl("gate", (f, d)), TensorDecl("up", (f, d)), TensorDecl("down", (d, f))]
+
+    def bind(self, tensors, dtype, device):
+        self.gate_up = torch.cat([tensors["gate"], tensors["up"]], dim=0).contiguous()
+        self.down = tensors["down"]
+        ops.declare_weights(self.gate_up, self.down)
+        self.dtype = dtype
+
+    def forward(self, ctx, h, residual):
+        t, f = h.shape[0], self.spec.intermediate
+        both = ctx.scratch("ffn.gate_up", (t, 2 * f), self.dtype)
+        ops.linear(h, self.gate_up, both)
+        act = ctx.scratch("ffn.act", (t, f), self.dtype)
+        ops.glu(both, act, self.limit, self.alpha, self.offset)
+        ops.linear(act, self.down, residual, accumulate=True, closes=ctx)
+
+
 class MixtureOfExperts(FeedForward):
     # Steps that hold a portion of a prompt read each expert's row count on the host (bfloat16
     # engine, see `forward`): such steps are not captured as graphs.  Decode steps are.
@@ -61,6 +99,11 @@ class MixtureOfExperts(FeedForward):
         self.top = int(spec.option("top", 0))
         self.ff = int(spec.intermediate)
         shared = spec.option("shared_intermediate")
+        self.has_bias = bool(spec.option("router_bias", False))
+        pair = spec.option("pair")
+        self.pair = tuple(float(v) for v in pair) if pair is not None else None
+        if self.pair is not None and (len(self.pair) != 3 or not self.pair[0] > 0):
+            raise ValueError("moe: pair is (limit > 0, alpha, offset)")
         if self.n <= 0 or not 0 < self.top <= self.n or self.ff <= 0:
             raise ValueError("moe: experts, top (at most experts) and the experts' ff must be positive")
         if self.n > 256 or self.top > 32:
@@ -71,6 +114,8 @@ class MixtureOfExperts(FeedForward):
     def tensors(self):
         d, f = self.spec.width, self.ff
         out = [TensorDecl("router", (self.n, d))]
+        if self.has_bias:
+            out.append(TensorDecl("router.b", (self.n,), role="vector", init=("normal", 0.0, 0.5)))
         for e in range(self.n):
             out += [TensorDecl(f"e{e}.gate", (f, d)), TensorDecl(f"e{e}.up", (f, d)),
                     TensorDecl(f"e{e}.down", (d, f))]
@@ -81,6 +126,7 @@ class MixtureOfExperts(FeedForward):
     def bind(self, tensors, dtype, device):
         self.dtype = dtype
         self.router = tensors["router"]
+        self.router_bias = tensors.get("router.b") if self.has_bias else None
         self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], 0)
                                     for e in range(self.n)], 0).contiguous()          # [E, 2F, d]
         self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.n)], 0).contiguous()   # [E, d, F]
@@ -100,7 +146,7 @@ class MixtureOfExperts(FeedForward):
         order = ctx.scratch("moe.order", (t * top,), torch.int32)
         weight = ctx.scratch("moe.weight", (t * top,), torch.float32)
         plan = ctx.scratch("moe.plan", (kernels.plan_ints(n, tiles),), torch.int32)
-        kernels.route(logits, top, idx, weight, place, self.count, plan, tiles, order)
+        kernels.route(logits, top, idx, weight, place, self.count, plan, tiles, order, bias=self.router_bias)
         act = ctx.scratch("moe.act", (t * top, f), self.dtype)
         pair_out = ctx.scratch("moe.pair_out", (t * top, d), torch.float32)
         if (self.dtype == torch.bfloat16 and t * top >= self.SORTED_MIN_PAIRS
@@ -111,20 +157,27 @@ class MixtureOfExperts(FeedForward):
             rows = ctx.scratch("moe.rows", (t * top, d), self.dtype)
             kernels.gather(h, order, top, rows)
             down = ctx.scratch("moe.down", (t * top, d), torch.float32)
+            both = ctx.scratch("moe.both", (t * top, 2 * f), self.dtype) if self.pair is not None else None
             for e in range(n):
                 a, b = starts[e], starts[e + 1]
                 if b > a:
-                    ops.linear_swiglu(rows[a:b], self.gate_up[e], act[a:b], ctx)
+                    if self.pair is None:
+                        ops.linear_swiglu(rows[a:b], self.gate_up[e], act[a:b], ctx)
+                    else:
+                        ops.linear(rows[a:b], self.gate_up[e], both[a:b])
+                        ops.glu(both[a:b], act[a:b], *self.pair)
                     ops.linear(act[a:b], self.down[e], down[a:b])
             kernels.scatter(down, order, weight, pair_out)
         elif (self.dtype == torch.bfloat16 and t * top <= self.SMALL_MAX_PAIRS
-              and kernels.expert_rows_small(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act)):
+              and kernels.expert_rows_small(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act,
+                                            pair=self.pair)):
             # few rows (decoded tokens): the weights are what moves; a warp per weight row
             if not kernels.expert_rows_small(False, act, self.down, d, plan, n, tiles, order, top, weight,
                                              pair_out):
                 kernels.expert_tiles(False, act, self.down, d, plan, n, tiles, order, top, weight, pair_out)
         else:
-            kernels.expert_tiles(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act)
+            kernels.expert_tiles(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act,
+                                 pair=self.pair)
             kernels.expert_tiles(False, act, self.down, d, plan, n, tiles, order, top, weight, pair_out)
         kernels.combine(pair_out, top, residual)
         if self.shared is not None:
@@ -132,4 +185,5 @@ class MixtureOfExperts(FeedForward):
 
 
 FEED_FORWARDS.register("dense_act", ActivatedFeedForward)
+FEED_FORWARDS.register("glu_capped", CappedGLU)
 FEED_FORWARDS.register("moe", MixtureOfExperts)

@@ -49,4 +49,19 @@ class RMSNorm(Norm):
         return run()
 
 
+class OffsetRMSNorm(RMSNorm):
+    """RMSNorm whose stored weight lies around zero: y = x * rsqrt(mean(x^2) + eps) * (1 + w).
+    The gain 1 + w is taken once at bind, as a float32 sum; everything else (the kernels, the
+    hand-over between products, the rows left un-normalised for a consumer's first product) is
+    the plain norm's."""
+
+    def tensors(self):
+        return [TensorDecl("gain", (self.spec.width,), role="vector", init=("normal", 0.0, 0.1))]
+
+    def bind(self, tensors, dtype, device):
+        super().bind(tensors, dtype, device)
+        self.gain = (tensors["gain"].to(torch.float32) + 1.0).contiguous()
+
+
 NORMS.register("rmsnorm", RMSNorm)
+NORMS.register("rmsnorm_offset", OffsetRMSNorm)

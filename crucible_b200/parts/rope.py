@@ -59,6 +59,8 @@ class InterleavedRotary(PositionEncoding):
     are float32 numbers and the angle is a float32 product taken in the kernel, so there
     is no table over positions and no longest position."""
 
+    split_halves = False       # which features pair: neighbours (2i, 2i + 1)
+
     def __init__(self, spec: PositionSpec):
         if spec.rotary_dim % 2 != 0 or spec.rotary_dim < 0:
             raise ValueError(f"rotary_dim must be even and not negative, got {spec.rotary_dim}")
@@ -87,6 +89,8 @@ class YarnRotary(PositionEncoding):
     and cos and sin are multiplied by 0.1 ln(factor) + 1 (`magnitude()`).  Without the options
     `factor`, `original`, `fast`, `slow` (the spec's `extra`) the frequencies are the base's and the
     magnitude is 1.  The angle is a float32 product of position and frequency taken in the kernel."""
+
+    split_halves = True        # which features pair: i with i + rotary_dim / 2
 
     def __init__(self, spec: PositionSpec, scaling=None):
         if spec.rotary_dim % 2 != 0 or spec.rotary_dim < 0:
@@ -122,3 +126,6 @@ class YarnRotary(PositionEncoding):
 
 
 POSITIONS.register("rope_yarn", lambda spec: YarnRotary(spec, spec.scaling))
+# split halves with the base's own frequencies and the angle taken in the kernel as an fp32
+# product (no table over positions, no longest position)
+POSITIONS.register("rope_halves", lambda spec: YarnRotary(spec, None))

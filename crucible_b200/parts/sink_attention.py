@@ -12,7 +12,11 @@ scaled.  The heads' results times sigmoid(h Wg^T) go through Wo.
 
 Options of the spec: value_dim (default head_dim), keep_first (default 0), sink
 (default true), value_norm_eps (None: values are cached as they are), gate (default
-true).  `window` None means every earlier key.
+true), qk_norm_eps (default None; a number: every q and k head is divided by its root mean
+square over D, that eps under the root, and multiplied by the weight `q.norm` / `k.norm` of
+size D that all heads share, before the rotation).  `window` None means every earlier key.
+The position encoding says which features pair (`split_halves`: i with i + R/2, else
+neighbours).
 """
 from __future__ import annotations
 
@@ -39,6 +43,7 @@ class SinkWindowAttention(BranchMixer):
         self.has_sink = bool(spec.option("sink", True))
         self.has_gate = bool(spec.option("gate", True))
         self.value_eps = spec.option("value_norm_eps")
+        self.qk_eps = spec.option("qk_norm_eps")
         if self.keep_first < 0 or self.value_dim <= 0:
             raise ValueError("keep_first must not be negative and value_dim must be positive")
         self.position = (POSITIONS.build(spec.position.kind, spec.position)
@@ -57,6 +62,9 @@ class SinkWindowAttention(BranchMixer):
             out.append(TensorDecl("g", (s.n_heads * self.value_dim, d)))
         if self.has_sink:
             out.append(TensorDecl("sink", (s.n_heads,), role="vector", init=("normal", 0.0, 1.0)))
+        if self.qk_eps is not None:
+            out += [TensorDecl("q.norm", (s.head_dim,), role="vector", init=("normal", 1.0, 0.1)),
+                    TensorDecl("k.norm", (s.head_dim,), role="vector", init=("normal", 1.0, 0.1))]
         return out
 
     def bind(self, tensors, dtype, device):
@@ -64,6 +72,8 @@ class SinkWindowAttention(BranchMixer):
         self.w_in = torch.cat(parts, dim=0).contiguous()
         self.w_out = tensors["o"]
         self.sinks = tensors.get("sink") if self.has_sink else None
+        self.q_gain = tensors.get("q.norm") if self.qk_eps is not None else None
+        self.k_gain = tensors.get("k.norm") if self.qk_eps is not None else None
         self.dtype = dtype
         self._declare()
         if self.position is not None:
@@ -79,10 +89,15 @@ class SinkWindowAttention(BranchMixer):
         s = self.spec
         cache = ctx.cache(binding.group)
         freq, rotary_dim = (self.position.frequencies() if self.position is not None else (None, 0))
-        if self.value_eps is None:
-            raise ValueError("this attention caches unit-rms values: value_norm_eps is needed")
-        kernels.rotate_norm_append(proj, freq, rotary_dim, s.n_heads, s.n_kv_heads, s.head_dim,
-                                   self.value_dim, float(self.value_eps), ctx, cache, binding)
+        split = bool(getattr(self.position, "split_halves", False))
+        if self.qk_eps is None and not split and self.value_eps is not None:
+            kernels.rotate_norm_append(proj, freq, rotary_dim, s.n_heads, s.n_kv_heads, s.head_dim,
+                                       self.value_dim, float(self.value_eps), ctx, cache, binding)
+        else:
+            kernels.norm_rotate_append(proj, self.q_gain, self.k_gain,
+                                       float(self.qk_eps) if self.qk_eps is not None else 0.0, freq,
+                                       rotary_dim, split, s.n_heads, s.n_kv_heads, s.head_dim,
+                                       self.value_dim, self.value_eps, ctx, cache, binding)
         q_width = s.n_heads * s.head_dim
         g_at = q_width + s.n_kv_heads * (s.head_dim + self.value_dim)
         gate = proj[:, g_at:g_at + s.n_heads * self.value_dim] if self.has_gate else None
