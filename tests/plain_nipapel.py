@@ -223,3 +223,14 @@ def read_folder(model_dir):
         else:
             raise ValueError(f"{name}: dtype {info['dtype']}")
     return cfg, out
+
+
+def greedy(cfg, weights, prompt, n_new, dtype=torch.float64):
+    """The prompt's continuation by the largest logit (the lower index on ties), the whole
+    sequence run again for every token."""
+    tokens, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(torch.argmax(forward(cfg, weights, tokens, dtype)[-1]))
+        out.append(nxt)
+        tokens.append(nxt)
+    return out
