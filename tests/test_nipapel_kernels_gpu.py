@@ -186,7 +186,7 @@ def test_attention_sees_exactly_its_keys(dtype, D, E, tensor_cores, how, window,
     from crucible_b200.ops import sink_attention as k
     from crucible_b200.parts import MIXERS, LayerBinding
     monkeypatch.setattr(k, "TENSOR_CORES", tensor_cores)
-    H, G, R, width, page, scale = 4, 2, 8, 48, 8, 0.5
+    H, G, R, width, page, scale = 4, 2, 8, 48, 8, 6.0 / D       # a marked key's score is D * scale
     marked = sorted({max(keep - 1, 0), keep, 7, 8, 40} | ({63, 64, 130} if T > 200 else set()))
 
     def edit(t):
