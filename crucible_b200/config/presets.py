@@ -99,3 +99,33 @@ def futepel(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab
 
 SHAPES["futepel-w1024"] = futepel(*COMPARISON_SIZES["w1024"])
 SHAPES["futepel-w2048"] = futepel(*COMPARISON_SIZES["w2048"])
+
+
+def nipapel(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int,
+            layers: int = 4, experts: int = 8, top: int = 2, window: int = 1024, keep_first: int = 4) -> dict:
+    """A Nipapel config.json of a real model's proportions: `layers` layers that take turns as
+    latent attention + dense feed-forward, attention + experts, latent attention that reads the
+    first one's cached rows + experts, attention + dense; every mixer `heads * head_dim` wide,
+    the latent's cached row 256 features (192 of latent, 64 rotated), the queries' latent half
+    the model's width, `experts` experts of half the dense width of which a token uses `top`."""
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff // 2, "limit": 7.0}}
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 192,
+              "q_rank": width // 2, "scale": (head_dim + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64},
+              "mask": {"size": window}}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                 "scale": head_dim ** -0.5, "rot": {"base": 10000.0, "dims": head_dim // 2},
+                 "mask": {"size": window, "keep_first": keep_first}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            out.append({"type": "latent_attention", "mixer": dict(latent), "mlp": dense})
+        elif i % 4 == 2:
+            out.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 2), "mlp": moe})
+        else:
+            out.append({"type": "attention", "mixer": dict(attention), "mlp": moe if i % 4 == 1 else dense})
+    return {"architecture": "Nipapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
+
+
+SHAPES["nipapel-w1024"] = nipapel(*COMPARISON_SIZES["w1024"])
+SHAPES["nipapel-w2048"] = nipapel(*COMPARISON_SIZES["w2048"])
