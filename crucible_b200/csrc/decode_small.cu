@@ -66,6 +66,7 @@ struct SmallParams {
     __nv_bfloat16* k_cache;
     __nv_bfloat16* v_cache;
     int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
+    float glu_limit, glu_alpha, glu_offset;   // SWIGLU: limit > 0: the capped pair instead of silu(g) * u
     int trigger_early;            // let the kernel after this one start as soon as this one's weights are asked for
                                   // (the q/k/v product: measured on B200 at batch 1 / 8, 2,048-token contexts,
                                   // 0.291 -> 0.286 / 0.345 -> 0.330 ms per step; for the other products 0 to
@@ -376,9 +377,16 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
                 if (ok_f) out[rf] = EPI == ACCUM_F32 ? old[nt][e] + df : df;
                 if (ok_s) out[rs] = EPI == ACCUM_F32 ? old[nt][2 + e] + ds : ds;
             } else if (EPI == SWIGLU_BF16) {
-                if (ok_f)
+                if (ok_f) {
+                    float gv = df, uv = ds, slope = 1.0f;
+                    if (p.glu_limit > 0.f) {      // g' = min(g, limit), u' = clamp(u) + offset, g' sigmoid(alpha g') u'
+                        gv = fminf(df, p.glu_limit);
+                        uv = fminf(fmaxf(ds, -p.glu_limit), p.glu_limit) + p.glu_offset;
+                        slope = p.glu_alpha;
+                    }
                     ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + rf] =
-                        __float2bfloat16_rn(df / (1.0f + expf(-df)) * ds);
+                        __float2bfloat16_rn(gv / (1.0f + expf(-slope * gv)) * uv);
+                }
             } else if (ok_f) {
                 const int half = p.head_dim >> 1;
                 const int pair = tile * 8 + g;
@@ -480,15 +488,17 @@ CB_EXPORT int cb_small_linear_bf16(const float* x, const float* gain, float eps,
 }
 
 // out[M, inter] (bf16) = silu(act Wg^T) * (act Wu^T), W = [Wg; Wu] ([2 inter, K]).
+// glu_limit > 0: the capped pair, min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + offset).
 CB_EXPORT int cb_small_swiglu(const float* x, const float* gain, float eps, const void* a, int lda,
                               const void* w, int ldw, void* out, int ldc, int M, int inter, int K,
-                              void* stream) {
+                              float glu_limit, float glu_alpha, float glu_offset, void* stream) {
     if (M <= 0 || inter <= 0) return 0;
     if (!sizes_ok(x, gain, a, lda, M, K, ldw, w)) return CB_ERR_UNSUPPORTED;
     SmallParams p = {};
     p.x = x; p.gain = gain; p.eps = eps; p.a = (const __nv_bfloat16*)a; p.lda = lda;
     p.w = (const __nv_bfloat16*)w; p.ldw = ldw; p.M = M; p.K = K; p.N = inter;
     p.n_tiles = (inter + 7) / 8; p.out = out; p.ldc = ldc;
+    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_offset = glu_offset;
     cudaStream_t s = (cudaStream_t)stream;
     return x ? launch_rows<true, SWIGLU_BF16>(p, s) : launch_rows<false, SWIGLU_BF16>(p, s);
 }

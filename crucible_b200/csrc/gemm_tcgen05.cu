@@ -10,7 +10,8 @@
 //   STORE_F32   C fp32 = acc                      (logits)
 //   ACCUM_F32   C fp32 += acc                     (residual add in 32 bits)
 //   SWIGLU_BF16 W = [Wg; Wu] ([2I, K]); the tile holds BN/2 gate rows and the
-//               BN/2 matching up rows; C[M, I] bf16 = silu(g) * u in fp32
+//               BN/2 matching up rows; C[M, I] bf16 = silu(g) * u in fp32, or the capped
+//               pair of the same two halves (NormArgs::glu_limit > 0)
 //
 // Many tiles and a long K (prompts at the larger layer sizes): 148 blocks of 128 x 256 ask
 // the L2 for more operand bytes than it delivers (384 rows of operands per 128 x 256 of
@@ -80,6 +81,15 @@ struct NormArgs {
     const float* sumsq_in;
     int parts;
     float width, eps;
+    // SWIGLU_BF16: limit > 0 makes the pair the capped one (tc::gated_pair), else silu(g) * u
+    float glu_limit, glu_alpha, glu_offset;
+    // A grouped product (plan != null): the rows of A lie expert by expert, W is the experts'
+    // matrices one below the other (w_rows rows each), and block row y takes tile y of the plan
+    // that a kernel before this one left on the device: [0] tiles in use, [2 + E + y] the tile's
+    // expert, [2 + E + max_tiles + y] its first row, [2 + E + 2 max_tiles + y] its rows (at most
+    // 128).  Tiles beyond those in use compute on rows they do not own and store nothing.
+    const int* plan;
+    int n_experts, max_tiles, w_rows;
 };
 
 template <int BN, int STAGES, int MH>
@@ -109,14 +119,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c,
                     const __grid_constant__ CUtensorMap map_s, int tma_out,
-                    void* __restrict__ c_ptr, int M, int N, int K, int ldc, int inter,
+                    void* __restrict__ c_ptr, int M_all, int N, int K, int ldc, int inter,
                     int k_splits, int* __restrict__ status, const RopeArgs ra, const NormArgs na) {
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES, MH>;
     Storage& s = *reinterpret_cast<Storage*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM * MH;
+    // (a grouped product learns its rows, their end and its expert's rows of W after the wait below)
+    int m0 = blockIdx.y * BM * MH, M = M_all, w_row0 = 0;
     const int n_tile = blockIdx.x;
     // this block's share of K: blocks of 64 elements [kb_first, kb_first + k_blocks)
     const uint32_t split = k_splits > 1 ? tc::cluster_rank() : 0u;
@@ -155,17 +166,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     auto load_w = [&](int kb, int st) {
         if (EPI == SWIGLU_BF16) {
             const int half = BN / 2;
-            tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * half);
+            tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, w_row0 + n_tile * half);
             tc::tma_load_2d(s.b[st] + half * BK * 2, &map_w, &s.full_bar[st], (kb_first + kb) * BK,
-                            inter + n_tile * half);
+                            w_row0 + inter + n_tile * half);
         } else {
-            tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, n_tile * BN);
+            tc::tma_load_2d(s.b[st], &map_w, &s.full_bar[st], (kb_first + kb) * BK, w_row0 + n_tile * BN);
         }
     };
     // Barriers, tensor memory and descriptors are ready.  The first stages' tiles of W go out
     // now: W is a weight matrix, which no kernel of the stream writes, so these copies need
     // not wait for the kernels before this one; A is their output and does.
-    const int w_ahead = k_blocks < STAGES ? k_blocks : STAGES;
+    // (not in a grouped product: which expert's W it is stands in the plan, which a kernel wrote)
+    const int w_ahead = na.plan != nullptr ? 0 : (k_blocks < STAGES ? k_blocks : STAGES);
     if (warp == 0 && lane == 0) {
         for (int kb = 0; kb < w_ahead; ++kb) {
             tc::mbar_expect_tx(&s.full_bar[kb], STAGE_BYTES);
@@ -174,6 +186,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     cb_pdl_wait();
     cb_pdl_trigger();
+    if (na.plan != nullptr) {
+        const int tile = blockIdx.y;
+        const int* entry = na.plan + 2 + na.n_experts + tile;
+        const bool in_use = tile < __ldg(na.plan);
+        m0 = in_use ? __ldg(entry + na.max_tiles) : 0;
+        M = in_use ? m0 + __ldg(entry + 2 * na.max_tiles) : 0;
+        w_row0 = in_use ? __ldg(entry) * na.w_rows : 0;
+    }
 
     // A norm after the product: the tile of C (32-column boxes in the 128-byte swizzle) comes
     // into its own piece of shared memory behind the stages, asked for by an epilogue thread
@@ -628,8 +648,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                 tc::tmem_ld_wait();
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
-                                    v[j] = __float_as_uint(tc::silu_fast(__uint_as_float(v[j]) * f) *
-                                                           (__uint_as_float(u[j]) * f));
+                                    v[j] = __float_as_uint(tc::gated_pair(__uint_as_float(v[j]) * f, __uint_as_float(u[j]) * f,
+                                                                          na.glu_limit, na.glu_alpha, na.glu_offset));
                             } else {
                                 tc::tmem_ld_wait();
                                 if (PRE) {
@@ -687,8 +707,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                             for (int j = 0; j < 8; ++j) {
                                 const float g0 = __uint_as_float(g[2 * j]) * rf[0];
                                 const float g1 = __uint_as_float(g[2 * j + 1]) * rf[0];
-                                const float h0 = tc::silu_fast(g0) * (__uint_as_float(u[2 * j]) * rf[0]);
-                                const float h1 = tc::silu_fast(g1) * (__uint_as_float(u[2 * j + 1]) * rf[0]);
+                                const float h0 = tc::gated_pair(g0, __uint_as_float(u[2 * j]) * rf[0], na.glu_limit,
+                                                                na.glu_alpha, na.glu_offset);
+                                const float h1 = tc::gated_pair(g1, __uint_as_float(u[2 * j + 1]) * rf[0], na.glu_limit,
+                                                                na.glu_alpha, na.glu_offset);
                                 __nv_bfloat162 v = __floats2bfloat162_rn(h0, h1);
                                 packed[j] = *reinterpret_cast<uint32_t*>(&v);
                             }
@@ -700,8 +722,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                             for (int j = 0; j < 16; ++j) {
                                 if (col0 + j < inter) {
                                     const float gv = __uint_as_float(g[j]) * rf[0];
-                                    dst[j] = __float2bfloat16_rn(tc::silu_fast(gv) *
-                                                                 (__uint_as_float(u[j]) * rf[0]));
+                                    dst[j] = __float2bfloat16_rn(tc::gated_pair(gv, __uint_as_float(u[j]) * rf[0], na.glu_limit,
+                                                                                na.glu_alpha, na.glu_offset));
                                 }
                             }
                         }
@@ -811,6 +833,10 @@ template <int BN, int STAGES, int EPI, int MH, int NORM>
 int launch_norm(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, int N, int K, int ldc,
                 int inter, int k_splits, int* status, cudaStream_t stream, const RopeArgs& ra, const NormArgs& na) {
     if (MH > 1 && k_splits > 1) return CB_ERR_UNSUPPORTED;
+    const bool grouped = na.plan != nullptr;
+    if (grouped && (MH > 1 || k_splits > 1 || NORM != NORM_NONE || EPI == ROPE_APPEND || EPI == ACCUM_F32 ||
+                    na.max_tiles <= 0 || na.w_rows <= 0))
+        return CB_ERR_UNSUPPORTED;
     // a norm after the product: only the epilogue that has the summed rows in registers leaves it
     const bool emit = na.gain != nullptr;
     using Storage = SharedStorage<BN, STAGES, MH>;
@@ -835,6 +861,7 @@ int launch_norm(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, in
     const int out_cols = EPI == SWIGLU_BF16 ? inter : N;
     int tma_out = ((uintptr_t)C & 15) == 0 && ((size_t)ldc * esize) % 16 == 0 &&
                   (f32 || (EPI == SWIGLU_BF16 ? BN % 128 == 0 : BN % 64 == 0));
+    if (grouped) tma_out = 0;        // a tile's rows end where its expert's do: every thread stores its own row
     CUtensorMap mc = ma;
     // ROPE_APPEND: only the q heads' columns of C are written
     const uint64_t map_cols = EPI == ROPE_APPEND ? (uint64_t)ra.n_heads * ra.head_dim : (uint64_t)out_cols;
@@ -853,7 +880,7 @@ int launch_norm(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, in
         configured = smem;
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
-    dim3 grid((n_cols + BN - 1) / BN, (M + BM * MH - 1) / (BM * MH), k_splits);
+    dim3 grid((n_cols + BN - 1) / BN, grouped ? na.max_tiles : (M + BM * MH - 1) / (BM * MH), k_splits);
     cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI, MH, NORM>, dim3(grid), dim3(192), smem, stream, k_splits,
                       ma, mw, mc, ms, tma_out, C, M, N, K, ldc, inter, k_splits, status, ra, na);
     return cb_last_error();
@@ -938,6 +965,36 @@ CB_EXPORT int cb_gemm_tcgen05(const void* A, const void* W, void* C, int M, int 
         case 160: return launch_epi<160, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
         case 192: return launch_epi<192, 5>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
         case 256: return launch_epi<256, 4>(epi, ma, mw, C, M, N, K, ldc, inter, k_splits, status, s, na);
+    }
+    return CB_ERR_UNSUPPORTED;
+}
+
+// The grouped product of a mixture of experts: A [M, K] holds the experts' rows expert by
+// expert, W [experts * w_rows, K] their matrices one below the other, and the plan on the device
+// says which rows are whose (NormArgs::plan and the fields after it, set by the caller in `norm`).
+// epi: STORE_BF16, STORE_F32 or SWIGLU_BF16 (N = the intermediate width, w_rows = 2 N).
+// bn: 64, 96 or 128.  Nothing of the plan is read on the host: a step replays as a graph.
+CB_EXPORT int cb_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int M, int N, int K, int lda,
+                                      int ldw, int ldc, int epi, int bn, int* status, void* stream,
+                                      const void* norm) {
+    if (M <= 0 || N <= 0) return 0;
+    if (norm == nullptr) return CB_ERR_UNSUPPORTED;
+    const NormArgs na = *static_cast<const NormArgs*>(norm);
+    if (na.plan == nullptr || na.n_experts <= 0 || na.gain != nullptr || na.sumsq_in != nullptr ||
+        K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+        return CB_ERR_UNSUPPORTED;
+    if (epi != STORE_BF16 && epi != STORE_F32 && epi != SWIGLU_BF16) return CB_ERR_UNSUPPORTED;
+    const int box_rows = epi == SWIGLU_BF16 ? bn / 2 : bn;
+    CUtensorMap ma, mw;
+    if (!tc::make_map_2d(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mw, W, (uint64_t)na.n_experts * (uint64_t)na.w_rows, (uint64_t)K, (uint64_t)ldw, box_rows))
+        return CB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int inter = epi == SWIGLU_BF16 ? N : 0;
+    switch (bn) {
+        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, 1, status, s, na);
+        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, 1, status, s, na);
+        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, 1, status, s, na);
     }
     return CB_ERR_UNSUPPORTED;
 }

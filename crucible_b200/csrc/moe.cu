@@ -78,11 +78,12 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
     }
 }
 
+// (tile_rows_: rows of a tile: TM for the kernels of this file, 128 for the tensor cores' grouped product)
 // plan: [0] number of tiles, [1 .. E+1] each expert's start in the sorted order, then
 // max_tiles each of (expert, start, rows).
 __global__ void moe_plan_kernel(int* __restrict__ count, int E, int n_pairs, const int* __restrict__ idx,
                                 const int* __restrict__ place, int* __restrict__ plan, int max_tiles,
-                                int* __restrict__ sorted_pair) {
+                                int* __restrict__ sorted_pair, int tile_rows_) {
     cb_pdl_trigger();
     cb_pdl_wait();
     int* offsets = plan + 1;
@@ -94,10 +95,10 @@ __global__ void moe_plan_kernel(int* __restrict__ count, int E, int n_pairs, con
         for (int e = 0; e < E; ++e) {
             offsets[e] = at;
             const int n = count[e];
-            for (int r = 0; r < n && tiles < max_tiles; r += TM, ++tiles) {
+            for (int r = 0; r < n && tiles < max_tiles; r += tile_rows_, ++tiles) {
                 tile_expert[tiles] = e;
                 tile_start[tiles] = at + r;
-                tile_rows[tiles] = min(TM, n - r);
+                tile_rows[tiles] = min(tile_rows_, n - r);
             }
             at += n;
         }
@@ -341,14 +342,14 @@ CB_EXPORT int cb_moe_tile_rows() { return TM; }
 CB_EXPORT int cb_moe_route(const float* logits, const float* bias, int n_tokens, int E, int top, int* idx,
                            float* weight,
                            int* place, int* count, int* plan, int max_tiles, int* sorted_pair,
-                           void* stream) {
+                           int tile_rows, void* stream) {
     if (n_tokens <= 0) return 0;
     if (E > 32 * MAX_PER_LANE || top > E || top <= 0 || top > 32) return CB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     cb_launch(moe_route_kernel, dim3((n_tokens + 3) / 4), dim3(128), 0, s, logits, bias, n_tokens, E, top, idx,
               weight, place, count);
     cb_launch(moe_plan_kernel, dim3(1), dim3(256), 0, s, count, E, n_tokens * top, (const int*)idx,
-              (const int*)place, plan, max_tiles, sorted_pair);
+              (const int*)place, plan, max_tiles, sorted_pair, tile_rows > 0 ? tile_rows : TM);
     return cb_last_error();
 }
 

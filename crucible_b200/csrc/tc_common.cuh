@@ -504,4 +504,21 @@ __device__ __forceinline__ float silu_fast(float g) {
     return fmaf(h, t, h);
 }
 
+// The gated pair of a feed-forward's two halves.  limit <= 0: silu(g) * u.  Else the capped
+// pair: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + offset),
+// with g' sigmoid(alpha g') = (g' / 2) (1 + tanh(alpha g' / 2)) by the same one trip to the
+// special-function unit.  `limit` is the same for every thread of a launch.
+__device__ __forceinline__ float gated_pair(float g, float u, float limit, float alpha, float offset) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + offset;
+        float t;
+        const float z = 0.5f * alpha * g;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(z));
+        const float h = 0.5f * g;
+        return fmaf(h, t, h) * u;
+    }
+    return silu_fast(g) * u;
+}
+
 }  // namespace tc

@@ -336,23 +336,27 @@ def _prenormed(h):
     return h if isinstance(h, small_batch.LazyNorm) and h.scaled is not None else None
 
 
-def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx) -> None:
-    """out[T, I] = silu(h Wg^T) * (h Wu^T) with gate_up = [Wg; Wu] of shape [2I, d]."""
+def linear_swiglu(h, gate_up: torch.Tensor, out: torch.Tensor, ctx, pair=None) -> None:
+    """out[T, I] = silu(h Wg^T) * (h Wu^T) with gate_up = [Wg; Wu] of shape [2I, d].  `pair` =
+    (limit, alpha, offset): the capped gated pair of the two halves instead (see `glu`)."""
     from . import small_batch
     if gate_up.dtype == torch.bfloat16 and is_weight(gate_up):
-        if h.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear_swiglu(h, gate_up, out):
+        if h.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear_swiglu(h, gate_up, out, pair=pair):
             return
         from . import tensor_core
         pre = _prenormed(h)
-        if pre is not None and tensor_core.linear_swiglu(pre.scaled, gate_up, out, pre=pre):
+        if pre is not None and tensor_core.linear_swiglu(pre.scaled, gate_up, out, pre=pre, pair=pair):
             return
         h = small_batch.as_tensor(h)
-        if tensor_core.linear_swiglu(h, gate_up, out):
+        if tensor_core.linear_swiglu(h, gate_up, out, pair=pair):
             return
     h = small_batch.as_tensor(h)
     both = ctx.scratch("ffn.gate_up", (h.shape[0], gate_up.shape[0]), h.dtype)
     linear(h, gate_up, both)
-    swiglu(both, out)
+    if pair is None:
+        swiglu(both, out)
+    else:
+        glu(both, out, *pair)
 
 
 def qkv_rope_append(h, wqkv: torch.Tensor, qkv: torch.Tensor, n_heads: int, n_kv_heads: int,

@@ -13,9 +13,13 @@ def tile_rows() -> int:
     return int(build.load("moe").cb_moe_tile_rows())
 
 
-def max_tiles(n_tokens: int, top: int, n_experts: int) -> int:
-    """An upper bound of the row tiles of a step: every expert may end on a partial tile."""
-    return -(-n_tokens * top // tile_rows()) + n_experts
+GROUPED_TILE_ROWS = 128      # rows of a tile of the tensor cores' grouped product
+
+
+def max_tiles(n_tokens: int, top: int, n_experts: int, rows: int = 0) -> int:
+    """An upper bound of the row tiles of a step: every expert may end on a partial tile.
+    `rows`: rows of a tile (0: those of this file's own kernels)."""
+    return -(-n_tokens * top // (rows or tile_rows())) + n_experts
 
 
 def plan_ints(n_experts: int, tiles: int) -> int:
@@ -28,10 +32,12 @@ def _pair(pair):
     return ctypes.c_float(limit), ctypes.c_float(alpha), ctypes.c_float(offset)
 
 
-def route(logits, top: int, idx, weight, place, count, plan, tiles: int, sorted_pair, bias=None) -> None:
+def route(logits, top: int, idx, weight, place, count, plan, tiles: int, sorted_pair, bias=None,
+          rows: int = 0) -> None:
     """Per token the `top` largest logits (plus `bias`, float32 [experts], if given; the lower
     index on ties) and their softmax; then
-    the sorted order of the (token, choice) pairs by expert and the tiles over it.  `count`
+    the sorted order of the (token, choice) pairs by expert and the tiles (of `rows` rows; 0: this
+    file's own) over it.  `count`
     (int32 [experts]) is zero between calls: the kernels leave it so."""
     _need_cuda(logits, idx, weight, place, count, plan, sorted_pair, bias)
     if logits.dtype != torch.float32 or not logits.is_contiguous():
@@ -44,7 +50,7 @@ def route(logits, top: int, idx, weight, place, count, plan, tiles: int, sorted_
     lib = build.load("moe")
     _check(lib.cb_moe_route(_ptr(logits), _ptr(bias), _c_int(t), _c_int(e), _c_int(top), _ptr(idx), _ptr(weight),
                             _ptr(place), _ptr(count), _ptr(plan), _c_int(tiles), _ptr(sorted_pair),
-                            _stream()), "moe route")
+                            _c_int(rows), _stream()), "moe route")
 
 
 def expert_tiles(gated: bool, a, w, n_out: int, plan, n_experts: int, tiles: int, sorted_pair, top: int,
@@ -110,3 +116,12 @@ def scatter(rows, sorted_pair, weight, pair_out) -> None:
     lib = build.load("moe")
     _check(lib.cb_moe_scatter(_ptr(rows), _ptr(sorted_pair), _ptr(weight), _ptr(pair_out),
                               _c_int(rows.shape[0]), _c_int(rows.shape[1]), _stream()), "moe scatter")
+
+
+def grouped_linear(rows_sorted, w, out, plan, n_experts: int, tiles: int, gated: bool, pair=None) -> bool:
+    """The experts' products over their rows side by side, on the tensor cores, by the plan on
+    the device (tiles of `GROUPED_TILE_ROWS` rows): out[i] = rows_sorted[i] . W[expert of row i]^T
+    with w [experts, N, K]; gated: w [experts, 2 F, K] and out [pairs, F] = the gated pair of
+    the two halves (`pair`: the capped form).  False: the sizes do not allow it."""
+    from . import tensor_core
+    return tensor_core.grouped_linear(rows_sorted, w, out, plan, n_experts, tiles, gated, pair)

@@ -135,7 +135,7 @@ def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = Fa
                                      _c_int(1 if accumulate else 0), _stream()), "small linear")
 
 
-def linear_swiglu(h: Rows, gate_up: torch.Tensor, out: torch.Tensor) -> bool:
+def linear_swiglu(h: Rows, gate_up: torch.Tensor, out: torch.Tensor, pair=None) -> bool:
     if (not _weights_ok(gate_up, h.shape[0]) or out.dtype != torch.bfloat16
             or out.stride(1) != 1):
         return False
@@ -148,6 +148,7 @@ def linear_swiglu(h: Rows, gate_up: torch.Tensor, out: torch.Tensor) -> bool:
                                      _ptr(gate_up), _c_int(gate_up.stride(0)), _ptr(out),
                                      _c_int(out.stride(0)), _c_int(h.shape[0]),
                                      _c_int(gate_up.shape[0] // 2), _c_int(gate_up.shape[1]),
+                                     *(_c_float(float(v)) for v in (pair or (0.0, 1.0, 0.0))),
                                      _stream()), "small swiglu")
 
 

@@ -178,7 +178,10 @@ class _NormArgs(ctypes.Structure):
     """`NormArgs` of csrc/gemm_tcgen05.cu."""
     _fields_ = [("gain", ctypes.c_void_p), ("scaled", ctypes.c_void_p), ("sumsq_out", ctypes.c_void_p),
                 ("ld_scaled", ctypes.c_int), ("sumsq_in", ctypes.c_void_p), ("parts", ctypes.c_int),
-                ("width", ctypes.c_float), ("eps", ctypes.c_float)]
+                ("width", ctypes.c_float), ("eps", ctypes.c_float),
+                ("glu_limit", ctypes.c_float), ("glu_alpha", ctypes.c_float), ("glu_offset", ctypes.c_float),
+                ("plan", ctypes.c_void_p), ("n_experts", ctypes.c_int), ("max_tiles", ctypes.c_int),
+                ("w_rows", ctypes.c_int)]
 
 
 class NormEmit:
@@ -193,11 +196,14 @@ class NormEmit:
         self.parts = None
 
 
-def _norm_args(emit, pre, rows: int):
-    """The pointer the product kernels take, and the object that keeps it alive."""
-    if emit is None and pre is None:
+def _norm_args(emit, pre, rows: int, pair=None):
+    """The pointer the product kernels take, and the object that keeps it alive.  `pair`:
+    (limit, alpha, offset) of the capped gated pair for the SwiGLU form."""
+    if emit is None and pre is None and pair is None:
         return _c_void_p(0), None
     args = _NormArgs()
+    if pair is not None:
+        args.glu_limit, args.glu_alpha, args.glu_offset = (float(v) for v in pair)
     if emit is not None:
         args.gain, args.scaled = emit.gain.data_ptr(), emit.scaled.data_ptr()
         args.sumsq_out, args.ld_scaled = emit.sumsq.data_ptr(), emit.scaled.stride(0)
@@ -209,11 +215,11 @@ def _norm_args(emit, pre, rows: int):
     return ctypes.cast(ctypes.pointer(args), _c_void_p), args
 
 
-def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None) -> bool:
+def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None, pair=None) -> bool:
     lib = build.load("gemm_tcgen05")
     if per_sm == 0:
         # 256 x 256 tiles; an output that cannot leave by TMA is refused, and the 128-row tiles run
-        if _gemm(a, w, out, n, epi, 256, -1, 1, None, pre):
+        if _gemm(a, w, out, n, epi, 256, -1, 1, None, pre, pair):
             return True
         per_sm = 1
     if per_sm == -1:
@@ -223,7 +229,7 @@ def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None) -> 
     if emit is not None and (epi != ACCUM_F32 or bn > NORM_AHEAD_MAX_TILE or per_sm == 0 or n % 32
                              or emit.sumsq.shape[0] < -(-n // bn) or emit.sumsq.stride(0) != a.shape[0]):
         emit = None
-    norm_ptr, keep = _norm_args(emit, pre, a.shape[0])
+    norm_ptr, keep = _norm_args(emit, pre, a.shape[0], pair)
     code = lib.cb_gemm_tcgen05(
         _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
         _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)),
@@ -341,18 +347,49 @@ def linear(a, w, out, *, accumulate=False, tile=None, emit=None, pre=None) -> bo
     return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None, emit, pre)
 
 
-def linear_swiglu(h, gate_up, out, tile=None, pre=None) -> bool:
+def grouped_linear(a, w, out, plan, n_experts: int, tiles: int, gated: bool, pair=None) -> bool:
+    """The grouped product of a mixture of experts (`cb_gemm_tcgen05_grouped`): `a` [pairs, K]
+    bfloat16 rows expert by expert, `w` [experts, rows, K] a declared weight, `plan` the int32
+    plan on the device with `tiles` tile entries of 128 rows.  gated: out [pairs, rows / 2]
+    bfloat16 with the gated pair; else out float32 or bfloat16 [pairs, rows]."""
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 3 or not w.is_contiguous()
+            or a.stride(1) != 1 or out.stride(1) != 1 or a.shape[1] != w.shape[2]):
+        return False
+    if gated and out.dtype != torch.bfloat16:
+        return False
+    epi = SWIGLU_BF16 if gated else (STORE_F32 if out.dtype == torch.float32 else STORE_BF16)
+    n = w.shape[1] // 2 if gated else w.shape[1]
+    args = _NormArgs()
+    if pair is not None:
+        args.glu_limit, args.glu_alpha, args.glu_offset = (float(v) for v in pair)
+    args.plan, args.n_experts, args.max_tiles, args.w_rows = plan.data_ptr(), n_experts, tiles, w.shape[1]
+    lib = build.load("gemm_tcgen05")
+    code = lib.cb_gemm_tcgen05_grouped(
+        _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
+        _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)), _c_int(w.stride(1)),
+        _c_int(out.stride(0)), _c_int(epi), _c_int(128), _c_void_p(status_word(a.device).data_ptr()),
+        _stream(), ctypes.cast(ctypes.pointer(args), _c_void_p))
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"grouped tensor-core product failed to launch (CUDA error {code})")
+    _count(1)
+    return True
+
+
+def linear_swiglu(h, gate_up, out, tile=None, pre=None, pair=None) -> bool:
+    """`pair`: (limit, alpha, offset): the capped gated pair instead of silu(g) * u."""
     if not _operands_ok(h, gate_up) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
         return False
     inter = gate_up.shape[0] // 2
     if tile is None and h.shape[0] <= SKINNY_ROWS and gate_up.numel() * 2 >= SKINNY_MIN_BYTES:
-        if pre is not None:
+        if pre is not None or pair is not None:      # (the few-row split product has the silu pair only)
             return False
         return _gemm_skinny(h, gate_up, out, inter, SWIGLU_BF16)
     if tile is None and _tall_tiles(h.shape[0], 2 * inter, h.shape[1]):
         tile = (256, 0)
     bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(h.shape[0], 2 * inter, SWIGLU_BF16)
-    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None, None, pre)
+    return _gemm(h, gate_up, out, inter, SWIGLU_BF16, bn, per_sm, splits[0] if splits else None, None, pre, pair)
 
 
 ROPE_TALL = None     # tests may fix the form of the q/k/v product (True: 256 x 256 tiles)

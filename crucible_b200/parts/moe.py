@@ -78,20 +78,17 @@ class CappedGLU(FeedForward):
 
     def forward(self, ctx, h, residual):
         t, f = h.shape[0], self.spec.intermediate
-        both = ctx.scratch("ffn.gate_up", (t, 2 * f), self.dtype)
-        ops.linear(h, self.gate_up, both)
         act = ctx.scratch("ffn.act", (t, f), self.dtype)
-        ops.glu(both, act, self.limit, self.alpha, self.offset)
+        ops.linear_swiglu(h, self.gate_up, act, ctx, pair=(self.limit, self.alpha, self.offset))
         ops.linear(act, self.down, residual, accumulate=True, closes=ctx)
 
 
 class MixtureOfExperts(FeedForward):
-    # Steps that hold a portion of a prompt read each expert's row count on the host (bfloat16
-    # engine, see `forward`): such steps are not captured as graphs.  Decode steps are.
-    graph_safe_prompt_steps = False
+    # Nothing of a step's routing comes to the host: the launches depend on the step's shape
+    # alone, so prompt steps are captured as graphs like decode steps.
     SMALL_MAX_PAIRS = 256        # up to this many pairs the experts' weight rows are read by a warp each
     SORTED_MIN_PAIRS = 256       # from this many (token, expert) pairs on, a prompt step's experts
-                                 # run as one product each over their rows side by side
+                                 # run as two grouped products over their rows side by side
 
     def __init__(self, spec: FeedForwardSpec):
         self.spec = spec
@@ -140,33 +137,28 @@ class MixtureOfExperts(FeedForward):
         t, d, top, n, f = h.shape[0], self.spec.width, self.top, self.n, self.ff
         logits = ctx.scratch("moe.logits", (t, n), torch.float32)
         ops.linear(h, self.router, logits)
-        tiles = kernels.max_tiles(t, top, n)
+        # many rows of a prompt: the experts' rows side by side and two grouped products on the
+        # tensor cores, by the plan on the device (tiles of 128 rows)
+        grouped = (self.dtype == torch.bfloat16 and t * top >= self.SORTED_MIN_PAIRS
+                   and ctx.host.max_new_tokens > 1 and d % 8 == 0 and f % 8 == 0)
+        tile_rows = kernels.GROUPED_TILE_ROWS if grouped else 0
+        tiles = kernels.max_tiles(t, top, n, tile_rows)
         idx = ctx.scratch("moe.idx", (t * top,), torch.int32)
         place = ctx.scratch("moe.place", (t * top,), torch.int32)
         order = ctx.scratch("moe.order", (t * top,), torch.int32)
         weight = ctx.scratch("moe.weight", (t * top,), torch.float32)
         plan = ctx.scratch("moe.plan", (kernels.plan_ints(n, tiles),), torch.int32)
-        kernels.route(logits, top, idx, weight, place, self.count, plan, tiles, order, bias=self.router_bias)
+        kernels.route(logits, top, idx, weight, place, self.count, plan, tiles, order, bias=self.router_bias,
+                      rows=tile_rows)
         act = ctx.scratch("moe.act", (t * top, f), self.dtype)
         pair_out = ctx.scratch("moe.pair_out", (t * top, d), torch.float32)
-        if (self.dtype == torch.bfloat16 and t * top >= self.SORTED_MIN_PAIRS
-                and ctx.host.max_new_tokens > 1 and not torch.cuda.is_current_stream_capturing()):
-            # many rows: each expert's rows side by side, one gate/up product with SiLU and one
-            # down product per expert on the tensor cores; the row counts come to the host
-            starts = plan[1:2 + n].tolist()
+        if grouped:
             rows = ctx.scratch("moe.rows", (t * top, d), self.dtype)
             kernels.gather(h, order, top, rows)
             down = ctx.scratch("moe.down", (t * top, d), torch.float32)
-            both = ctx.scratch("moe.both", (t * top, 2 * f), self.dtype) if self.pair is not None else None
-            for e in range(n):
-                a, b = starts[e], starts[e + 1]
-                if b > a:
-                    if self.pair is None:
-                        ops.linear_swiglu(rows[a:b], self.gate_up[e], act[a:b], ctx)
-                    else:
-                        ops.linear(rows[a:b], self.gate_up[e], both[a:b])
-                        ops.glu(both[a:b], act[a:b], *self.pair)
-                    ops.linear(act[a:b], self.down[e], down[a:b])
+            if not (kernels.grouped_linear(rows, self.gate_up, act, plan, n, tiles, True, pair=self.pair)
+                    and kernels.grouped_linear(act, self.down, down, plan, n, tiles, False)):
+                raise RuntimeError("moe: the grouped product refused sizes its rule allows")
             kernels.scatter(down, order, weight, pair_out)
         elif (self.dtype == torch.bfloat16 and t * top <= self.SMALL_MAX_PAIRS
               and kernels.expert_rows_small(True, h, self.gate_up, f, plan, n, tiles, order, top, weight, act,
