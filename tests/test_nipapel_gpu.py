@@ -92,6 +92,17 @@ def test_steps_are_replayed_as_graphs(tmp_path):
     _compare("ni-a", "bfloat16", got, _reference(model_dir, requests))
 
 
+def test_prompt_steps_with_experts_are_replayed_as_graphs(tmp_path):
+    """Portions of a fixed size repeat their shape: from the second time on they are replayed,
+    experts and all (nothing of the routing comes to the host)."""
+    model_dir = _folder(tmp_path, "ni-c", "bfloat16")
+    requests = {"r0": helpers.random_tokens(400, 6 * 160 + 3, 1)}
+    engine, got = _replay("ni-c", "bfloat16", model_dir, _portions(requests, [160]), str(tmp_path / "o"), 1024)
+    assert not engine._graph_failed, engine._graph_error
+    assert engine._prompt_graph_replays >= 2
+    _compare("ni-c", "bfloat16", got, _reference(model_dir, requests))
+
+
 def test_long_decoding_past_every_window(tmp_path):
     """Two tokens of prompt, then 300 decoded ones: every window passes over decoded tokens many
     times, the pages behind it go back to the pool while the kept first tokens' pages stay."""

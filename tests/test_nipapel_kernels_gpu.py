@@ -372,3 +372,44 @@ def test_latent_gate_and_query_norm_matter():
     assert rel(plain.latent_attention(h, open_gate, cfg, 1e-5, pos, rows), ref) > 0.1
     flat = dict(w); flat["dq.norm"] = torch.ones(Q, dtype=torch.float64)
     assert rel(plain.latent_attention(h, flat, cfg, 1e-5, pos, rows), ref) > 0.02
+
+
+# ---------------------------------------------------------------------------
+# the experts of a prompt step as grouped products on the tensor cores
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("experts,top,ff,width,rows", [(8, 2, 64, 128, 700), (5, 1, 40, 64, 300), (3, 3, 72, 48, 129)])
+def test_grouped_products_follow_the_plan_on_the_device(experts, top, ff, width, rows, monkeypatch):
+    """Many rows in bfloat16: the rows lie expert by expert and two grouped products run over
+    tiles of 128 rows whose owners the device alone knows.  Experts with no rows, with one row
+    and with more than a tile's worth all occur; the result is the plain one, and nothing of the
+    step comes to the host (no per-expert product is launched)."""
+    from crucible_b200 import ops
+    from crucible_b200.config.model_config import FeedForwardSpec
+    from crucible_b200.ops import moe as kernels
+    from crucible_b200.parts import FEED_FORWARDS
+    dtype = torch.bfloat16
+    spec = FeedForwardSpec(kind="moe", width=width, intermediate=ff,
+                           extra=(("experts", experts), ("top", top), ("shared_intermediate", None),
+                                  ("router_bias", True), ("pair", (1.0, 1.702, 1.0))))
+    part = FEED_FORWARDS.build("moe", spec)
+
+    def edit(t):
+        # expert 0 gets no token at all (unless all are used), the last one a single token
+        bias = torch.linspace(1.0, 3.0, experts)
+        bias[0] = -50.0 if top < experts else 0.0
+        t["router.b"] = bias
+        t["router"] *= 0.02
+    w = _bind(part, dtype, seed=4, edit=edit)
+    cfg = {"router": {"experts": experts, "top": top}, "expert": {"ff": ff, "limit": 1.0}}
+    h = torch.randn(rows, width, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).float()
+    ref = plain.experts(h.double(), w, cfg)
+    calls = {"grouped": 0, "linear": 0}
+    grouped, linear = kernels.grouped_linear, ops.linear
+    monkeypatch.setattr(kernels, "grouped_linear", lambda *a, **k: calls.__setitem__("grouped", calls["grouped"] + 1) or grouped(*a, **k))
+    monkeypatch.setattr(ops, "linear", lambda *a, **k: calls.__setitem__("linear", calls["linear"] + 1) or linear(*a, **k))
+    res = torch.zeros(rows, width, device=DEV)
+    part.forward(Steps(dtype).ctx([(0, rows)], None), h.to(dtype).to(DEV), res)
+    assert rel(res, ref) < TOL[dtype]
+    assert calls == {"grouped": 2, "linear": 1}          # the router's logits and the two grouped products
+    assert part.count.tolist() == [0] * experts          # left ready for the next step
