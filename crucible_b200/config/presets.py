@@ -102,7 +102,7 @@ SHAPES["futepel-w2048"] = futepel(*COMPARISON_SIZES["w2048"])
 
 
 def nipapel(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int,
-            layers: int = 4, experts: int = 8, top: int = 2, window: int = 1024, keep_first: int = 4) -> dict:
+            layers: int = 4, experts: int = 8, top: int = 2, window: int = 1024, keep_first: int = 8) -> dict:
     """A Nipapel config.json of a real model's proportions: `layers` layers that take turns as
     latent attention + dense feed-forward, attention + experts, latent attention that reads the
     first one's cached rows + experts, attention + dense; every mixer `heads * head_dim` wide,

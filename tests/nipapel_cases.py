@@ -53,14 +53,14 @@ CASES = {
         "architecture": "Nipapel", "vocab": 211, "width": 44, "norm": {"eps": 1e-5},
         "layers": [latent(1, 10, 6, 14, 21, 9, 0.3, 100.0, 40, moe(1, 1, 20, 0.5)),
                    latent(5, 4, 6, 6, 21, 13, 0.5, 100.0, 40, None, kv_from=0),
-                   attention(3, 1, 12, 12, 0.35, 4, 20000.0, 17, 17, dense(52, 1.0)),
+                   attention(3, 1, 12, 12, 0.35, 4, 3000.0, 17, 17, dense(52, 1.1)),
                    latent(2, 12, 6, 10, 21, 30, 0.3, 100.0, 7, moe(3, 3, 12, 2.0), kv_from=0)]}),
     # sizes that let the bfloat16 products and both attentions run on the tensor cores
     "ni-c": dict(seed=5, page_tokens=16, config={
         "architecture": "Nipapel", "vocab": 400, "width": 128, "norm": {"eps": 1e-5},
-        "layers": [latent(4, 32, 32, 32, 96, 64, 0.15, 20000.0, 70, moe(8, 3, 64, 2.0)),
-                   attention(4, 2, 64, 64, 0.125, 32, 50000.0, 70, 5, dense(256, 1.0)),
-                   latent(4, 32, 32, 32, 96, 64, 0.15, 20000.0, 70, moe(8, 3, 64, 2.0), kv_from=0)]}),
+        "layers": [latent(4, 32, 32, 32, 96, 64, 0.15, 9000.0, 70, moe(8, 2, 80, 1.7)),
+                   attention(4, 2, 64, 64, 0.11, 48, 40000.0, 70, 5, dense(272, 0.9)),
+                   latent(4, 32, 32, 32, 96, 64, 0.15, 9000.0, 70, moe(8, 2, 80, 1.7), kv_from=0)]}),
 }
 
 
