@@ -49,7 +49,7 @@ struct AttnParams {
     int window;            // 0: all earlier keys
     float* partial;        // split kernel: [rows_total * n_heads][n_chunks][head_dim + 2]
     int n_chunks;
-    int chunk_keys;        // split kernel: keys per chunk, a multiple of SPLIT_KEYS
+    int chunk_keys;        // split kernel: keys per chunk, a multiple of SPLIT_KEYS (of 64 for rows wider than 128)
     // The extended tiles form (EXT): a window that keeps the first tokens visible, a sink per
     // head in the softmax's denominator, and a sigmoid output gate with a scale.
     int keep_first;        // with a window: keys below this stay visible to every later row
@@ -949,7 +949,7 @@ CB_EXPORT long cb_attention_split_counters(int n_requests, int n_kv_heads, int m
 }
 
 // n_chunks == 0: tiles kernel.  n_chunks > 0: split kernel over that many
-// chunks of chunk_keys keys (a multiple of 256; together they must cover the
+// chunks of chunk_keys keys (a multiple of 256, or of 64 for rows wider than 128; together they must cover the
 // longest context); `partial` must hold
 // cb_attention_split_scratch_floats floats and `counters`
 // cb_attention_split_counters zeroed ints.
@@ -1005,7 +1005,10 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
         else rc = launch_tiles<256>(p, n_requests, q_tiles, s);
         return rc;
     }
-    if (partial == nullptr || counters == nullptr || (chunk_keys % SPLIT_KEYS) != 0)
+    // a chunk is whole sub-tiles for each of the four warps: 4 x 16 keys for rows of more than
+    // 128 features, whole tiles of SPLIT_KEYS otherwise
+    if (partial == nullptr || counters == nullptr ||
+        (chunk_keys % (head_dim > 128 ? 4 * SplitShape<256>::SUB : SPLIT_KEYS)) != 0)
         return CB_ERR_UNSUPPORTED;
     const int q_tiles = (max_rows + 15) / 16;
     if (head_dim <= 16) rc = launch_split<16>(p, n_requests, q_tiles, counters, s);

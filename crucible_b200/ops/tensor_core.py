@@ -555,6 +555,25 @@ def decode_chunk_keys(blocks_per_chunk: int, context_bucket: int, tcgen05: bool,
     return min(max(chunk, unit), whole)
 
 
+WIDE_ROW_TARGET_BLOCKS = 2 * N_SMS
+
+
+def wide_row_chunk_keys(blocks_per_chunk: int, context_bucket: int, window) -> int:
+    """Keys per block of the mma.sync split attention over rows of more than 128 features (one
+    block to an SM; each of its four warps walks its sub-tiles of 16 keys one memory round trip
+    after the other, so short chunks are what hides the latency).  Chunks lie at fixed places
+    of the context; with a window only those that it touches work, so the working blocks are
+    counted over the window's reach: as many parts as bring them nearest to two per SM, in
+    whole tiles of 64 keys (one sub-tile a warp).  A function of the step's shape alone."""
+    unit = 64
+    reach = context_bucket if not window else min(context_bucket, window + unit)
+    parts = max(1, (2 * WIDE_ROW_TARGET_BLOCKS + blocks_per_chunk) // (2 * max(1, blocks_per_chunk)))
+    chunk = -(-reach // parts)
+    chunk = -(-chunk // unit) * unit
+    whole = -(-context_bucket // unit) * unit
+    return min(max(chunk, unit), whole)
+
+
 SPLIT_ROWS = 16          # packed rows (new tokens x heads of a group) the split form takes
 
 
@@ -572,7 +591,10 @@ def _attend(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, sca
     if split:
         groups = -(-reqs.max_new * n_rep // 16)
         blocks_per_chunk = reqs.count * n_kv_heads * groups
-        chunk_keys = decode_chunk_keys(blocks_per_chunk, reqs.bucket, decode_tc, head_dim)
+        if head_dim > 128:
+            chunk_keys = wide_row_chunk_keys(blocks_per_chunk, reqs.bucket, window)
+        else:
+            chunk_keys = decode_chunk_keys(blocks_per_chunk, reqs.bucket, decode_tc, head_dim)
         n_chunks = -(-reqs.bucket // chunk_keys)
         floats = reqs.rows_end * n_heads * n_chunks * (head_dim + 2)
         partial = ctx.scratch("attn.partial", (floats,), torch.float32)
@@ -587,8 +609,8 @@ def _attend(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, sca
             and _attention_tcgen05(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads,
                                    head_dim, scale, window, cache)):
         return True
-    if split and chunk_keys % 256:
-        # the mma.sync split form walks whole tiles of 256 keys
+    if split and head_dim <= 128 and chunk_keys % 256:
+        # the mma.sync split form of rows up to 128 features walks whole tiles of 256 keys
         chunk_keys = -(-chunk_keys // 256) * 256
         n_chunks = -(-reqs.bucket // chunk_keys)
     lib = build.load("attention_mma")

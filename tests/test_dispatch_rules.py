@@ -70,6 +70,28 @@ def test_decode_chunks_of_the_benchmark_points():
     assert tensor_core.decode_chunk_keys(16 * 8, 2304, True, 128) == 2304  # a block per request and KV head
 
 
+@pytest.mark.parametrize("blocks", [1, 3, 8, 40, 64, 300])
+@pytest.mark.parametrize("bucket", [256, 768, 2304, 16640])
+@pytest.mark.parametrize("window", [None, 1, 100, 1024, 50000])
+def test_wide_row_chunks_are_whole_tiles_of_64_that_cover_the_bucket(blocks, bucket, window):
+    chunk = tensor_core.wide_row_chunk_keys(blocks, bucket, window)
+    assert chunk % 64 == 0 and 64 <= chunk <= bucket
+    n_chunks = -(-bucket // chunk)
+    assert (n_chunks - 1) * chunk < bucket <= n_chunks * chunk     # no chunk is empty
+    # the blocks that a window lets work are not far more than two to an SM, unless a chunk is one tile
+    reach = bucket if not window else min(bucket, window + 64)
+    working = blocks * (-(-reach // chunk) + 1)
+    assert working <= 2 * tensor_core.WIDE_ROW_TARGET_BLOCKS + 2 * blocks or chunk == 64
+
+
+def test_wide_row_chunks_of_the_benchmark_points():
+    # a latent row of 256 features, one key head, contexts of 2,056 to 2,304 tokens, a window of 1,024
+    assert tensor_core.wide_row_chunk_keys(8, 2304, 1024) == 64        # 17 working chunks a request, 136 blocks
+    assert tensor_core.wide_row_chunk_keys(64, 2304, 1024) == 256      # 5 working chunks, 320 blocks
+    assert tensor_core.wide_row_chunk_keys(8, 2304, None) == 64        # 36 chunks, 288 blocks
+    assert tensor_core.wide_row_chunk_keys(64, 2304, None) == 512      # 5 chunks, 320 blocks
+
+
 def test_step_shape_key_follows_what_launches_depend_on():
     from crucible_b200.engine.context import HostStep
     decode = HostStep(list("abc"), [1, 1, 1], [2100, 300, 40], [2101, 301, 41], [0, 1, 2])

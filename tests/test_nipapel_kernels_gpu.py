@@ -284,6 +284,7 @@ def _mark_latent(H, D, R, C, Q, width):
                          [(2, 24, 8, 16, 40, 24, 48, 8, 21),
                           (4, 32, 32, 32, 96, 64, 64, 16, 70),          # rows of 128: tensor cores in bfloat16
                           (2, 16, 16, 16, 48, 8, 32, 8, 300),           # rows of 64; a window wider than the requests
+                          (4, 64, 64, 64, 192, 96, 128, 16, 130),       # rows of 256: decoded tokens' keys in chunks of 64
                           (3, 10, 6, 14, 21, 9, 40, 4, 5)])
 def test_latent_attention_finds_marked_keys(dtype, H, D, R, E, C, Q, width, page, window):
     marked = [2, page - 1, page, 3 * page - 1, 3 * page, 150, 263]
