@@ -90,6 +90,11 @@ struct NormArgs {
     // 128).  Tiles beyond those in use compute on rows they do not own and store nothing.
     const int* plan;
     int n_experts, max_tiles, w_rows;
+    // A product per head in one launch (heads > 0; not with a plan): block z takes head z, whose
+    // columns of A start at z * head_a_cols, whose matrix is rows [z * w_rows, z * w_rows + N) of
+    // W and whose results go to columns z * head_c_cols + [0, N) of C.  K is a head's K; what a
+    // block of 64 columns of A holds beyond it meets columns of W outside its map, which read zero.
+    int heads, head_a_cols, head_c_cols;
 };
 
 template <int BN, int STAGES, int MH>
@@ -119,7 +124,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_c,
                     const __grid_constant__ CUtensorMap map_s, int tma_out,
-                    void* __restrict__ c_ptr, int M_all, int N, int K, int ldc, int inter,
+                    void* c_ptr, int M_all, int N, int K, int ldc, int inter,
                     int k_splits, int* __restrict__ status, const RopeArgs ra, const NormArgs na) {
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES, MH>;
@@ -129,6 +134,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     // (a grouped product learns its rows, their end and its expert's rows of W after the wait below)
     int m0 = blockIdx.y * BM * MH, M = M_all, w_row0 = 0;
     const int n_tile = blockIdx.x;
+    // a product per head: this block's head moves the columns of A, the rows of W and the columns of C
+    const int head = na.heads > 0 ? (int)blockIdx.z : 0;
+    const int a_col0 = head * na.head_a_cols;
+    if (na.heads > 0) {
+        w_row0 = head * na.w_rows;
+        c_ptr = reinterpret_cast<uint8_t*>(c_ptr) +
+                (size_t)head * na.head_c_cols * ((EPI == STORE_F32 || EPI == ACCUM_F32) ? 4 : 2);
+    }
     // this block's share of K: blocks of 64 elements [kb_first, kb_first + k_blocks)
     const uint32_t split = k_splits > 1 ? tc::cluster_rank() : 0u;
     const int k_blocks_all = (K + BK - 1) / BK;
@@ -233,8 +246,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                 }
 #pragma unroll
                 for (int mh = 0; mh < MH; ++mh)
-                    tc::tma_load_2d(s.a[st] + mh * (BM * BK * 2), &map_a, &s.full_bar[st], (kb_first + kb) * BK,
-                                    m0 + mh * BM);
+                    tc::tma_load_2d(s.a[st] + mh * (BM * BK * 2), &map_a, &s.full_bar[st],
+                                    a_col0 + (kb_first + kb) * BK, m0 + mh * BM);
                 if (kb + 1 > armed) armed = kb + 1;
                 if (++st == STAGES) st = 0, parity ^= 1;
             }
@@ -862,6 +875,14 @@ int launch_norm(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, in
     int tma_out = ((uintptr_t)C & 15) == 0 && ((size_t)ldc * esize) % 16 == 0 &&
                   (f32 || (EPI == SWIGLU_BF16 ? BN % 128 == 0 : BN % 64 == 0));
     if (grouped) tma_out = 0;        // a tile's rows end where its expert's do: every thread stores its own row
+    const bool per_head = na.heads > 0;
+    if (per_head) {
+        // the heads' columns of C lie side by side: every thread stores its own row, 16 bytes at a time
+        if (grouped || MH > 1 || k_splits > 1 || NORM != NORM_NONE || (EPI != STORE_BF16 && EPI != STORE_F32) ||
+            na.w_rows <= 0 || (na.head_a_cols & 7) || ((size_t)na.head_c_cols * esize) % 16 || na.heads > 65535)
+            return CB_ERR_UNSUPPORTED;
+        tma_out = 0;
+    }
     CUtensorMap mc = ma;
     // ROPE_APPEND: only the q heads' columns of C are written
     const uint64_t map_cols = EPI == ROPE_APPEND ? (uint64_t)ra.n_heads * ra.head_dim : (uint64_t)out_cols;
@@ -880,7 +901,8 @@ int launch_norm(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int M, in
         configured = smem;
     }
     const int n_cols = EPI == SWIGLU_BF16 ? 2 * inter : N;
-    dim3 grid((n_cols + BN - 1) / BN, grouped ? na.max_tiles : (M + BM * MH - 1) / (BM * MH), k_splits);
+    dim3 grid((n_cols + BN - 1) / BN, grouped ? na.max_tiles : (M + BM * MH - 1) / (BM * MH),
+              per_head ? na.heads : k_splits);
     cb_launch_cluster(gemm_tcgen05_kernel<BN, STAGES, EPI, MH, NORM>, dim3(grid), dim3(192), smem, stream, k_splits,
                       ma, mw, mc, ms, tma_out, C, M, N, K, ldc, inter, k_splits, status, ra, na);
     return cb_last_error();
@@ -995,6 +1017,31 @@ CB_EXPORT int cb_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int
         case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, inter, 1, status, s, na);
         case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, inter, 1, status, s, na);
         case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, inter, 1, status, s, na);
+    }
+    return CB_ERR_UNSUPPORTED;
+}
+
+// A product per head in one launch: A [M, a_cols] holds head h's K columns from h * head_a_cols,
+// W [heads * N, K] the heads' matrices one below the other, and head h's results go to columns
+// h * head_c_cols + [0, N) of C (bf16 or fp32 by epi: STORE_BF16 or STORE_F32).  bn: 64, 96 or 128.
+CB_EXPORT int cb_gemm_tcgen05_heads(const void* A, const void* W, void* C, int M, int N, int K, int a_cols,
+                                    int lda, int ldw, int ldc, int heads, int head_a_cols, int head_c_cols,
+                                    int epi, int bn, int* status, void* stream) {
+    if (M <= 0 || N <= 0 || heads <= 0) return 0;
+    if (K <= 0 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) ||
+        ((uintptr_t)C & 15) || a_cols < (heads - 1) * head_a_cols + K)
+        return CB_ERR_UNSUPPORTED;
+    if (epi != STORE_BF16 && epi != STORE_F32) return CB_ERR_UNSUPPORTED;
+    NormArgs na{};
+    na.heads = heads; na.head_a_cols = head_a_cols; na.head_c_cols = head_c_cols; na.w_rows = N;
+    CUtensorMap ma, mw;
+    if (!tc::make_map_2d(&ma, A, (uint64_t)M, (uint64_t)a_cols, (uint64_t)lda, BM)) return CB_ERR_UNSUPPORTED;
+    if (!tc::make_map_2d(&mw, W, (uint64_t)heads * (uint64_t)N, (uint64_t)K, (uint64_t)ldw, bn)) return CB_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (bn) {
+        case 64: return launch_epi<64, 6>(epi, ma, mw, C, M, N, K, ldc, 0, 1, status, s, na);
+        case 96: return launch_epi<96, 6>(epi, ma, mw, C, M, N, K, ldc, 0, 1, status, s, na);
+        case 128: return launch_epi<128, 5>(epi, ma, mw, C, M, N, K, ldc, 0, 1, status, s, na);
     }
     return CB_ERR_UNSUPPORTED;
 }

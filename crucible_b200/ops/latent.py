@@ -61,13 +61,16 @@ def rows_gate(x, g) -> None:
 
 
 SMALL_ROWS = 16      # steps of up to this many rows take the heads' products in one launch
+HEADS_IN_ONE_LAUNCH = True   # many bfloat16 rows: the heads as the third axis of one tensor-core launch
+                             # (tests switch it off to reach the product per head with the same inputs)
 
 
 def heads_linear(a, a_head: int, w, out, out_head: int, gate_logit=None, gate_rows=None) -> None:
     """out[t, h * out_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head h of
     `w` [heads, N, K].  Steps of a few bfloat16 rows run as one launch whose warps each read one
-    weight row once; otherwise one product per head through `ops.linear` (the tensor-core tiles
-    for many bfloat16 rows; in float32 always, so that a row's sums never depend on the step).
+    weight row once; many bfloat16 rows as one launch of tensor-core tiles with the head as the
+    grid's third axis; otherwise one product per head through `ops.linear` (in float32 always, so
+    that a row's sums never depend on the step).
     `gate_logit` (float32 [rows, heads]): every head's results times sigmoid(logit), in the same
     launch for few rows, by `head_gate` otherwise.  `gate_rows` (rows of the activations' dtype,
     [rows, heads * N]): every result times the sigmoid of its own logit, likewise."""
@@ -91,8 +94,11 @@ def heads_linear(a, a_head: int, w, out, out_head: int, gate_logit=None, gate_ro
                                          _stream()),
                "heads_linear (few rows)")
         return
-    for i in range(heads):
-        linear(a[:, i * a_head:i * a_head + k], w[i], out[:, i * out_head:i * out_head + n])
+    from . import is_weight, tensor_core
+    if not (HEADS_IN_ONE_LAUNCH and a.dtype == torch.bfloat16 and is_weight(w)
+            and tensor_core.heads_linear(a, a_head, w, out, out_head)):
+        for i in range(heads):
+            linear(a[:, i * a_head:i * a_head + k], w[i], out[:, i * out_head:i * out_head + n])
     if gate_logit is not None:
         if out.shape[1] != heads * out_head:
             raise KernelError("heads_linear: a gate needs the heads' results side by side")

@@ -181,7 +181,8 @@ class _NormArgs(ctypes.Structure):
                 ("width", ctypes.c_float), ("eps", ctypes.c_float),
                 ("glu_limit", ctypes.c_float), ("glu_alpha", ctypes.c_float), ("glu_offset", ctypes.c_float),
                 ("plan", ctypes.c_void_p), ("n_experts", ctypes.c_int), ("max_tiles", ctypes.c_int),
-                ("w_rows", ctypes.c_int)]
+                ("w_rows", ctypes.c_int), ("heads", ctypes.c_int), ("head_a_cols", ctypes.c_int),
+                ("head_c_cols", ctypes.c_int)]
 
 
 class NormEmit:
@@ -373,6 +374,38 @@ def grouped_linear(a, w, out, plan, n_experts: int, tiles: int, gated: bool, pai
         return False
     if code != 0:
         raise RuntimeError(f"grouped tensor-core product failed to launch (CUDA error {code})")
+    _count(1)
+    return True
+
+
+HEADS_MIN_ROWS = 33      # from this many rows on the heads' products run as tiles of 128 rows
+
+
+def heads_linear(a, a_head: int, w, out, out_head: int) -> bool:
+    """out[t, h * out_head + n] = sum_k a[t, h * a_head + k] * w[h, n, k] for every head of `w`
+    [heads, N, K] (a declared bfloat16 weight) in ONE launch (`cb_gemm_tcgen05_heads`: the head is
+    the grid's third axis).  Refuses what the tiles cannot take (the caller then runs a product
+    per head)."""
+    heads, n, k = w.shape
+    if (a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or not a.is_cuda
+            or a.stride(1) != 1 or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32)
+            or a.shape[0] < HEADS_MIN_ROWS or k % 8 or a_head % 8 or a.stride(0) % 8
+            or a.data_ptr() % 16 or w.data_ptr() % 16 or out.data_ptr() % 16
+            or (out_head * out.element_size()) % 16 or (out.stride(0) * out.element_size()) % 16
+            or a.shape[1] < (heads - 1) * a_head + k or out.shape[1] < (heads - 1) * out_head + n):
+        return False
+    epi = STORE_F32 if out.dtype == torch.float32 else STORE_BF16
+    bn = 128 if n > 96 else (96 if n > 64 else 64)
+    lib = build.load("gemm_tcgen05")
+    code = lib.cb_gemm_tcgen05_heads(
+        _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()), _c_int(a.shape[0]),
+        _c_int(n), _c_int(k), _c_int(a.shape[1]), _c_int(a.stride(0)), _c_int(w.stride(1)),
+        _c_int(out.stride(0)), _c_int(heads), _c_int(a_head), _c_int(out_head), _c_int(epi), _c_int(bn),
+        _c_void_p(status_word(a.device).data_ptr()), _stream())
+    if code == _UNSUPPORTED:
+        return False
+    if code != 0:
+        raise RuntimeError(f"tensor-core product per head failed to launch (CUDA error {code})")
     _count(1)
     return True
 

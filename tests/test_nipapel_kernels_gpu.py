@@ -414,3 +414,35 @@ def test_grouped_products_follow_the_plan_on_the_device(experts, top, ff, width,
     assert rel(res, ref) < TOL[dtype]
     assert calls == {"grouped": 2, "linear": 1}          # the router's logits and the two grouped products
     assert part.count.tolist() == [0] * experts          # left ready for the next step
+
+
+@pytest.mark.parametrize("rows,heads,a_head,k,n,out_head", [(200, 4, 96, 64, 96, 96), (2048, 8, 192, 128, 192, 256),
+                                                            (333, 3, 256, 192, 40, 40), (129, 5, 72, 72, 136, 136),
+                                                            (64, 1, 64, 64, 64, 64)])
+@pytest.mark.parametrize("result", [torch.bfloat16, torch.float32])
+def test_heads_products_of_many_rows_are_one_launch(rows, heads, a_head, k, n, out_head, result):
+    """Every head's own matrix over its own columns of the rows, the head as the grid's third
+    axis: against the sums in float64, and counted.  Sizes whose K is no multiple of 64 (the
+    block's last columns belong to the next head and must meet zeros) and whose N is no
+    multiple of the tile (the tile's last rows of W belong to the next head and are not stored);
+    the columns between the heads' results stay as they were."""
+    from crucible_b200 import ops
+    from crucible_b200.ops import latent, tensor_core
+    g = torch.Generator().manual_seed(rows + heads)
+    a = torch.randn(rows, heads * a_head, generator=g).to(torch.bfloat16)
+    w = (torch.randn(heads, n, k, generator=g) * 0.2).to(torch.bfloat16)
+    ref = torch.einsum("thk,hnk->thn", a.double().view(rows, heads, a_head)[..., :k], w.double())
+    wd = w.to(DEV).contiguous()
+    ops.declare_weights(wd)
+    if result == torch.float32:
+        out = torch.full((rows, heads * out_head), 7.0, device=DEV, dtype=result)
+        assert tensor_core.heads_linear(a.to(DEV), a_head, wd, out, out_head)
+    else:
+        out = torch.full((rows, heads * out_head), 7.0, device=DEV, dtype=result)
+        before = ops.LAUNCHES[0]
+        latent.heads_linear(a.to(DEV), a_head, wd, out, out_head)
+        assert ops.LAUNCHES[0] - before == 1
+    got = out.double().cpu().view(rows, heads, out_head)
+    assert rel(got[..., :n], ref) < 1e-2
+    if out_head > n:
+        assert torch.all(got[..., n:] == 7.0)
