@@ -57,6 +57,7 @@ struct TcAttnParams {
     int n_heads, n_kv_heads, n_rep, n_requests, page_tokens, page_shift;
     float scale_log2;
     int window;
+    int keep_first;          // with a window: keys before this position stay visible to every later row
     int n_pages;             // of the pool
     int runs;                // 1: the 4-D maps may be used for tiles whose pages are consecutive
     int* status;
@@ -201,17 +202,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
     int key_lo = p.window > 0 ? max(0, min_pos - p.window + 1) : 0;
     key_lo = key_lo / KEYS * KEYS;
     const int key_end = max_pos + 1;
-    const int n_tiles = active ? (key_end - key_lo + KEYS - 1) / KEYS : 0;
+    // kept first tokens: their tiles that lie wholly before the window's first tile come first
+    // (those inside it are part of the window's own tiles and only change the mask)
+    const int kept_tiles = (active && p.window > 0 && p.keep_first > 0)
+                               ? min((p.keep_first + KEYS - 1) / KEYS, key_lo / KEYS) : 0;
+    const int n_tiles = active ? kept_tiles + (key_end - key_lo + KEYS - 1) / KEYS : 0;
+    auto tile_key0 = [&](int j) { return j < kept_tiles ? j * KEYS : key_lo + (j - kept_tiles) * KEYS; };
+    // a kept tile's pages beyond the last kept token's may have gone back to the pool: their
+    // keys are masked, and they are read from the last kept page instead
+    const int last_kept_page = p.keep_first > 0 ? (p.keep_first - 1) >> p.page_shift : 0;
 
     // ---- the loader's thread: one tile of K and V pages into a stage --------------------------
     const int pages_per_tile = KEYS >> p.page_shift;
     auto lookup = [&](int j, int (&pages)[16]) {
         // the tile's table entries, all in flight at once: the copies are ordered against
         // memory and would take the lookups one by one
-        const int key0 = key_lo + j * KEYS;
+        const int key0 = tile_key0(j);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             int index = (key0 >> p.page_shift) + (i < pages_per_tile ? i : 0);
+            if (j < kept_tiles && index > last_kept_page) index = last_kept_page;
             index = index < p.table_stride ? index : p.table_stride - 1;
             const int page = table[index];
             pages[i] = page < 0 ? 0 : page;           // an entry given back early: never read
@@ -457,7 +467,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             return __all_sync(0xffffffffu, got);
         };
         for (int j = group; j < n_tiles && ok; j += GROUPS) {
-            const int key0 = key_lo + j * KEYS;
+            const int key0 = tile_key0(j);
             const int b = j % S_BUFS;                 // the scores' buffer
             const int pb = j % PB;                    // P's buffer
             ok = wait_all(&s.s_full[b], (j / S_BUFS) & 1);
@@ -478,13 +488,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k,
             // lie wholly inside every row's range and skip the test.
             const int last = min(pos - key0, KEYS - 1);
             const int first = max(lo - key0, 0);
+            const int kept = p.keep_first - key0;     // keys before this one are kept first tokens (<= 0: none here)
             if (!__all_sync(0xffffffffu, last == KEYS - 1 && first == 0)) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int kk = c * 32 + i;
-                        if (kk > last || kk < first) sv[c][i] = __float_as_uint(-INFINITY);
+                        if (kk > last || (kk < first && kk >= kept)) sv[c][i] = __float_as_uint(-INFINITY);
                     }
             }
             float mc[4];
@@ -667,14 +678,16 @@ int launch_as(dim3 grid, cudaStream_t st, const CUtensorMap& mk, const CUtensorM
 
 // Attention for the rows of a step whose requests bring portions of prompts.
 // k_cache / v_cache: [n_pages][n_kv_heads][page_tokens][head_dim] bf16; head_dim 64 or 128.
-CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, int out_stride,
-                                   const void* k_cache, const void* v_cache, int n_pages,
-                                   const int* req_row_start, const int* req_first_pos,
-                                   const int* block_table, int table_stride, int n_requests,
-                                   int max_new_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                   int page_tokens, float scale, int window, int lean, int* status,
-                                   void* stream) {
+// keep_first (with a window): a row at position p reads j <= p with p - j < window or j < keep_first.
+CB_EXPORT int cb_attention_tcgen05_kept(const void* qkv, int qkv_stride, void* out, int out_stride,
+                                        const void* k_cache, const void* v_cache, int n_pages,
+                                        const int* req_row_start, const int* req_first_pos,
+                                        const int* block_table, int table_stride, int n_requests,
+                                        int max_new_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                        int page_tokens, float scale, int window, int keep_first, int lean,
+                                        int* status, void* stream) {
     if (n_requests <= 0 || max_new_tokens <= 0) return 0;
+    if (keep_first < 0 || !(scale > 0.f)) return CB_ERR_UNSUPPORTED;
     if ((head_dim != 64 && head_dim != 128) || n_heads % n_kv_heads != 0 || page_tokens < 8 || page_tokens > KEYS ||
         (page_tokens & (page_tokens - 1)) || (qkv_stride & 7) || (out_stride & 7) ||
         ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || ((uintptr_t)k_cache & 15) ||
@@ -711,6 +724,7 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
     p.page_shift = shift;
     p.scale_log2 = scale * LOG2E;
     p.window = window;
+    p.keep_first = window > 0 ? keep_first : 0;
     p.status = status;
     const int n_rep = n_heads / n_kv_heads;
     const int q_tiles = (max_new_tokens * n_rep + ROWS - 1) / ROWS;
@@ -726,4 +740,16 @@ CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, i
         return lean ? launch_as<64, true>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p)
                     : launch_as<64, false>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p);
     return launch_as<128, false>(grid, (cudaStream_t)stream, mk, mv, rk, rv, p);
+}
+
+CB_EXPORT int cb_attention_tcgen05(const void* qkv, int qkv_stride, void* out, int out_stride,
+                                   const void* k_cache, const void* v_cache, int n_pages,
+                                   const int* req_row_start, const int* req_first_pos,
+                                   const int* block_table, int table_stride, int n_requests,
+                                   int max_new_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                   int page_tokens, float scale, int window, int lean, int* status,
+                                   void* stream) {
+    return cb_attention_tcgen05_kept(qkv, qkv_stride, out, out_stride, k_cache, v_cache, n_pages, req_row_start,
+                                     req_first_pos, block_table, table_stride, n_requests, max_new_tokens, n_heads,
+                                     n_kv_heads, head_dim, page_tokens, scale, window, 0, lean, status, stream);
 }

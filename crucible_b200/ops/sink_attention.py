@@ -101,16 +101,24 @@ TENSOR_CORES = True      # tests switch it off to reach the plain kernel with th
 
 def _tensor_cores(q, gate, out, sinks, n_heads, n_kv_heads, key_dim, value_dim, scale, window,
                   keep_first, out_scale, ctx, cache, k_cache, v_cache, table) -> bool:
-    """The mma.sync kernel of 64-row tiles (`csrc/attention_mma.cu`, its extended form) for
-    bfloat16 rows whose keys and values have one size, a multiple of 16 up to 256: prompts'
-    portions and decoded tokens in one launch, the rows of a request's query heads that
-    share a key/value head packed into tiles.  Refuses anything else."""
+    """For bfloat16 rows whose keys and values have one size: steps of prompts' portions alone
+    with plain softmax and heads of 64 or 128 take the tcgen05 attention (`csrc/attention_tcgen05.cu`);
+    everything else of a size that is a multiple of 16 up to 256 the mma.sync kernel of 64-row
+    tiles (`csrc/attention_mma.cu`, its extended form): prompts' portions and decoded tokens in
+    one launch, the rows of a request's query heads that share a key/value head packed into
+    tiles.  Refuses anything else."""
     host = getattr(ctx, "host", None)
     if (not TENSOR_CORES or q.dtype != torch.bfloat16 or key_dim != value_dim or key_dim % 16
             or key_dim > 256 or host is None or q.stride(0) % 8 or out.stride(0) % 2
             or (gate is not None and gate.stride(0) % 2)):
         return False
-    from . import tensor_core  # noqa: F401  (registers the module)
+    from . import tensor_core
+    # a plain softmax over keys and values of 64 or 128 features, portions of prompts only: the
+    # tcgen05 attention, whose tiles take the kept first tokens ahead of the window's
+    if (sinks is None and gate is None and out_scale == 1.0
+            and tensor_core.prompt_attention(q, out, k_cache, v_cache, n_heads, n_kv_heads, key_dim, scale,
+                                             window, keep_first, ctx, cache, table)):
+        return True
     lib = build.load("attention_mma")
     # Few rows per request (decoded tokens, short portions): one row tile each, so the blocks
     # are few; the key tiles are then dealt to several blocks and merged.  The number of shares

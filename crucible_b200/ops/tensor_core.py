@@ -489,21 +489,22 @@ class _Requests:
 
 
 def _attention_tcgen05(qkv, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, scale,
-                       window, cache) -> bool:
+                       window, cache, keep_first: int = 0) -> bool:
     """tcgen05 attention for portions of prompts: head size 64 or 128, page size a
-    power of two from 8 to 128.  Returns False for anything else."""
+    power of two from 8 to 128.  `keep_first` (with a window): keys before that position stay
+    visible.  Returns False for anything else."""
     pt = cache.page_tokens
     if pt < 8 or pt > 128 or pt & (pt - 1):
         return False
     lib = build.load("attention_tcgen05")
-    code = lib.cb_attention_tcgen05(
+    code = lib.cb_attention_tcgen05_kept(
         _c_void_p(qkv.data_ptr()), _c_int(qkv.stride(0)), _c_void_p(out.data_ptr()),
         _c_int(out.stride(0)), _c_void_p(k_cache.data_ptr()), _c_void_p(v_cache.data_ptr()),
         _c_int(k_cache.shape[0]), _c_void_p(reqs.row_start.data_ptr()),
         _c_void_p(reqs.first_pos.data_ptr()), _c_void_p(reqs.table.data_ptr()),
         _c_int(reqs.table_stride), _c_int(reqs.count), _c_int(reqs.max_new),
         _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(pt),
-        ctypes.c_float(scale), _c_int(window or 0), _c_int(ATTENTION_LEAN),
+        ctypes.c_float(scale), _c_int(window or 0), _c_int(keep_first if window else 0), _c_int(ATTENTION_LEAN),
         _c_void_p(status_word(qkv.device).data_ptr()), _stream())
     if code == _UNSUPPORTED:
         return False
@@ -605,6 +606,24 @@ def wide_row_chunk_keys(blocks_per_chunk: int, context_bucket: int, window) -> i
     chunk = -(-chunk // unit) * unit
     whole = -(-context_bucket // unit) * unit
     return min(max(chunk, unit), whole)
+
+
+def prompt_attention(q, out, k_cache, v_cache, n_heads, n_kv_heads, head_dim, scale, window, keep_first,
+                     ctx, cache, table) -> bool:
+    """The tcgen05 attention for a step that holds portions of prompts only (no single decoded
+    tokens ahead of them) over keys and values of one size, 64 or 128, with a window that may
+    keep the first tokens: plain softmax, no gate.  `q`: rows of n_heads * head_dim.  False:
+    not taken."""
+    host = getattr(ctx, "host", None)
+    n_rep = n_heads // n_kv_heads
+    if (not USE_TCGEN05_ATTENTION or host is None or q.dtype != torch.bfloat16 or head_dim not in (64, 128)
+            or k_cache.dtype != torch.bfloat16 or host.lead_single != 0 or host.max_new_tokens * n_rep < 64
+            or q.stride(0) % 8 or out.stride(0) % 8 or q.data_ptr() % 16 or out.data_ptr() % 16
+            or k_cache.shape[-1] != head_dim or v_cache.shape[-1] != head_dim):
+        return False
+    reqs = _Requests(ctx, table, 0, ctx.n_requests, host.max_new_tokens, host.context_bucket, ctx.n_tokens)
+    return _attention_tcgen05(q, out, k_cache, v_cache, reqs, n_heads, n_kv_heads, head_dim, scale, window, cache,
+                              keep_first=keep_first)
 
 
 SPLIT_ROWS = 16          # packed rows (new tokens x heads of a group) the split form takes

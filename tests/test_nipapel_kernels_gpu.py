@@ -175,9 +175,11 @@ def _cuts(T, how):
 
 
 @pytest.mark.parametrize("dtype,D,E,tensor_cores", [(torch.float32, 16, 24, False), (torch.bfloat16, 16, 24, False),
-                                                    (torch.bfloat16, 32, 32, False), (torch.bfloat16, 32, 32, True)])
+                                                    (torch.bfloat16, 32, 32, False), (torch.bfloat16, 32, 32, True),
+                                                    # heads of 64 and 128: portions of 32 tokens and more on the tcgen05 tiles
+                                                    (torch.bfloat16, 64, 64, True), (torch.bfloat16, 128, 128, True)])
 @pytest.mark.parametrize("how", ["prompt", "portions", "decode"])
-@pytest.mark.parametrize("window,keep,T", [(10, 3, 90), (70, 5, 300), (33, 0, 120)])
+@pytest.mark.parametrize("window,keep,T", [(10, 3, 90), (70, 5, 300), (33, 0, 120), (40, 130, 420)])
 def test_attention_sees_exactly_its_keys(dtype, D, E, tensor_cores, how, window, keep, T, monkeypatch):
     """Feature 0 of the input is 1 for every token and feature 1 is large for a few marked
     tokens.  A channel that is not turned reads feature 0 in every query head and feature 1
