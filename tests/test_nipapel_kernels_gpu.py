@@ -448,3 +448,37 @@ def test_heads_products_of_many_rows_are_one_launch(rows, heads, a_head, k, n, o
     assert rel(got[..., :n], ref) < 1e-2
     if out_head > n:
         assert torch.all(got[..., n:] == 7.0)
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("window,keep", [(70, 5), (40, 130), (200, 0)])
+def test_unequal_portions_of_several_requests_in_one_step(D, window, keep, monkeypatch):
+    """Steps of portions alone, of unequal sizes, from three requests whose pages are scattered:
+    bfloat16 heads of 64 and 128 take the tensor-core tiles with the kept first tokens' tile
+    ahead of the window's; every request agrees with the plain attention over itself alone,
+    and a request that comes back in a later step goes on from its own keys."""
+    from crucible_b200.parts import MIXERS, LayerBinding
+    dtype, H, G, R, width, page = torch.bfloat16, 6, 3, D // 2, 64, 16
+    spec = _attention_spec(H, G, D, D, R, window, keep, width, D ** -0.5)
+    part = MIXERS.build(spec.kind, spec)
+    w = _bind(part, dtype, seed=6, std=0.2)
+    lengths = {0: 400, 1: 150, 2: 333}
+    g = torch.Generator().manual_seed(12)
+    h_of = {slot: torch.randn(n, width, generator=g).to(torch.bfloat16).float() for slot, n in lengths.items()}
+    cfg = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"base": 700.0, "dims": R},
+           "mask": {"size": window, "keep_first": keep}}
+    steps = StepsWithValues(dtype, part.cache_need(), page, 3, 400 + page)
+    binding = LayerBinding(group=0, slot=0, write=True)
+    schedule = [[(0, 200), (1, 40), (2, 33)], [(2, 300), (0, 100)], [(1, 110), (0, 100)]]
+    from crucible_b200.ops import tensor_core
+    taken, inner = [], tensor_core._attention_tcgen05
+
+    def counted(*args, **kwargs):
+        taken.append(inner(*args, **kwargs))
+        return taken[-1]
+    monkeypatch.setattr(tensor_core, "_attention_tcgen05", counted)
+    got = _run_part(part, steps, schedule, h_of, width, binding)
+    assert taken == [True, True, True]           # every step ran on the tcgen05 tiles
+    for slot, n in lengths.items():
+        ref = plain.attention(h_of[slot].double(), w, cfg, 1e-5, torch.arange(n))
+        assert rel(got[slot], ref) < TOL[dtype], slot
