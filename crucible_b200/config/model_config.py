@@ -126,9 +126,15 @@ class EndSpec:
 @dataclass(frozen=True)
 class RunEntry:
     """One entry of the run order: run stored layer `layer`; if `cache_of` is
-    set, its mixer reads (and does not write) the cache that layer owns."""
+    set, its mixer reads (and does not write) the cache that layer owns.
+    `copy`: a layer that runs several times with the same weights but with keys and
+    state of its own each time names a different copy in each of its entries (a
+    reader reads the copy of the same number).  `add`: (name of one of the model's
+    `vectors`, row): that row is added to the residual rows before the layer runs."""
     layer: int
     cache_of: Optional[int] = None
+    copy: int = 0
+    add: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -143,6 +149,9 @@ class ModelConfig:
     final_norm: NormSpec
     embedding: EndSpec = EndSpec("token")
     head: EndSpec = EndSpec("linear")
+    # tables of the model itself, each (name, rows) of float32 rows as wide as the model;
+    # a run-order entry may add one of their rows to the residual (`RunEntry.add`)
+    vectors: Tuple[Tuple[str, int], ...] = ()
     tensor_names: Mapping[str, str] = field(default_factory=dict, compare=False)
     raw: Mapping[str, Any] = field(default_factory=dict, compare=False)
 
@@ -163,6 +172,13 @@ class ModelConfig:
             if entry.cache_of is not None and not 0 <= entry.cache_of < len(self.layers):
                 raise ConfigError(f"run_order[{i}] reads the cache of layer "
                                   f"{entry.cache_of}, which does not exist")
+            if entry.copy < 0:
+                raise ConfigError(f"run_order[{i}] names copy {entry.copy}")
+            if entry.add is not None:
+                rows = dict(self.vectors).get(entry.add[0])
+                if rows is None or not 0 <= entry.add[1] < rows:
+                    raise ConfigError(f"run_order[{i}] adds row {entry.add[1]} of {entry.add[0]!r}, "
+                                      f"which the model's vectors do not hold")
         for i, layer in enumerate(self.layers):
             names = [name for name, _ in layer.norms]
             if len(set(names)) != len(names):

@@ -85,4 +85,4 @@ def _ensure_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from ..models import crucible_gpt, futepel, nipapel, vuvosun  # noqa: F401  (register on import)
+        from ..models import crucible_gpt, futepel, nipapel, sebalorn, vuvosun  # noqa: F401  (register on import)

@@ -56,6 +56,7 @@ struct AttnParams {
     const float* sinks;    // [n_heads], natural-log units, or null
     const __nv_bfloat16* gate;   // rows of gate logits laid out like `out`, or null
     int gate_stride;
+    int gate_per_head;           // 1: a gate row holds one logit per head instead
     float out_scale;
 };
 
@@ -523,7 +524,12 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
             if (row_a < n_rows) {
                 const int tok = row_base + row_a / n_rep, head = kv_head * n_rep + row_a % n_rep;
                 float x = o[n][0] * inv_a, y = o[n][1] * inv_a;
-                if (EXT && p.gate != nullptr) {
+                if (EXT && p.gate != nullptr && p.gate_per_head) {
+                    const float g = 1.0f / (1.0f + __expf(-__bfloat162float(
+                                                p.gate[(size_t)tok * p.gate_stride + head])));
+                    x *= g;
+                    y *= g;
+                } else if (EXT && p.gate != nullptr) {
                     const __nv_bfloat162 gt = *reinterpret_cast<const __nv_bfloat162*>(
                         p.gate + (size_t)tok * p.gate_stride + (size_t)head * p.head_dim + col);
                     x *= 1.0f / (1.0f + __expf(-__bfloat162float(gt.x)));
@@ -535,7 +541,12 @@ __global__ void __launch_bounds__(128) attention_tiles_kernel(const AttnParams p
             if (row_b < n_rows) {
                 const int tok = row_base + row_b / n_rep, head = kv_head * n_rep + row_b % n_rep;
                 float x = o[n][2] * inv_b, y = o[n][3] * inv_b;
-                if (EXT && p.gate != nullptr) {
+                if (EXT && p.gate != nullptr && p.gate_per_head) {
+                    const float g = 1.0f / (1.0f + __expf(-__bfloat162float(
+                                                p.gate[(size_t)tok * p.gate_stride + head])));
+                    x *= g;
+                    y *= g;
+                } else if (EXT && p.gate != nullptr) {
                     const __nv_bfloat162 gt = *reinterpret_cast<const __nv_bfloat162*>(
                         p.gate + (size_t)tok * p.gate_stride + (size_t)head * p.head_dim + col);
                     x *= 1.0f / (1.0f + __expf(-__bfloat162float(gt.x)));
@@ -873,7 +884,8 @@ __global__ void __launch_bounds__(128) attention_merge_kernel(const AttnParams p
             float x = acc[i] * inv;
             if (p.gate != nullptr)
                 x *= 1.0f / (1.0f + __expf(-__bfloat162float(
-                                       p.gate[(size_t)tok * p.gate_stride + (size_t)head * hd + f])));
+                                       p.gate[(size_t)tok * p.gate_stride +
+                                              (p.gate_per_head ? (size_t)head : (size_t)head * hd + f)])));
             p.out[(size_t)tok * p.out_stride + (size_t)head * hd + f] = __float2bfloat16_rn(x);
         }
     }
@@ -988,6 +1000,7 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
     p.sinks = nullptr;
     p.gate = nullptr;
     p.gate_stride = 0;
+    p.gate_per_head = 0;
     p.out_scale = 1.0f;
     p.partial = partial;
     p.n_chunks = n_chunks;
@@ -1022,7 +1035,8 @@ CB_EXPORT int cb_attention_mma(const void* qkv, int qkv_stride, void* out, int o
 // The extended tiles form, for prompts' portions and decoded tokens alike: a row at position p
 // sees j <= p with p - j < window or j < keep_first (window 0: every earlier key); sinks
 // ([n_heads], may be null) join each head's denominator as exp(sink); the result is multiplied
-// by sigmoid(gate) (rows laid out like `out`, may be null) and by out_scale.  q: rows of
+// by sigmoid(gate) (rows laid out like `out`, or one logit per head with gate_per_head; may be
+// null) and by out_scale.  q: rows of
 // n_heads * head_dim at q_stride.  Keys and values have the same size.  n_chunks > 1 (requests
 // of at most 64 packed rows): the key tiles in that many shares over blocks, and a merge.
 CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int out_stride,
@@ -1032,11 +1046,11 @@ CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int 
                                     int n_requests, int max_new_tokens, int n_heads, int n_kv_heads,
                                     int head_dim, int page_tokens, float scale, int window,
                                     int keep_first, float out_scale, float* partial, int n_chunks,
-                                    void* stream) {
+                                    int gate_per_head, void* stream) {
     if (n_requests <= 0 || max_new_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > 256 || (head_dim & 15) || n_heads % n_kv_heads != 0 ||
-        (q_stride & 7) || (out_stride & 1) || (gate_stride & 1) || ((uintptr_t)q & 15) ||
-        ((uintptr_t)out & 3) || ((uintptr_t)gate & 3) || ((uintptr_t)k_cache & 15) ||
+        (q_stride & 7) || (out_stride & 1) || (!gate_per_head && (gate_stride & 1)) || ((uintptr_t)q & 15) ||
+        ((uintptr_t)out & 3) || (!gate_per_head && ((uintptr_t)gate & 3)) || ((uintptr_t)k_cache & 15) ||
         ((uintptr_t)v_cache & 15) || keep_first < 0)
         return CB_ERR_UNSUPPORTED;
     AttnParams p;
@@ -1060,6 +1074,7 @@ CB_EXPORT int cb_attention_mma_sink(const void* q, int q_stride, void* out, int 
     p.sinks = sinks;
     p.gate = (const __nv_bfloat16*)gate;
     p.gate_stride = gate_stride;
+    p.gate_per_head = gate != nullptr && gate_per_head ? 1 : 0;
     p.out_scale = out_scale;
     p.partial = partial;
     p.n_chunks = n_chunks;

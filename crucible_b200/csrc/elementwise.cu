@@ -256,6 +256,40 @@ CB_EXPORT int cb_gather_rows(const float* x, const int* rows, float* out, int n_
 }
 
 // ---------------------------------------------------------------------------
+// x[t, :] += v[:] for every row of the fp32 residual (a learned vector added to all tokens),
+// and the soft cap of fp32 rows in place: z <- cap * tanh(z / cap).
+// ---------------------------------------------------------------------------
+__global__ void add_vector_kernel(float* __restrict__ x, const float* __restrict__ v, int width) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    float* row = x + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) row[i] += v[i];
+}
+
+CB_EXPORT int cb_add_vector(float* x, const float* v, int n_rows, int width, void* stream) {
+    if (n_rows <= 0) return 0;
+    cb_launch(add_vector_kernel, dim3(n_rows), dim3(width >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, x, v,
+              width);
+    return cb_last_error();
+}
+
+__global__ void softcap_kernel(float* __restrict__ z, int width, float cap, float inv_cap) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    float* row = z + (size_t)blockIdx.y * width;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < width) row[i] = cap * tanhf(row[i] * inv_cap);
+}
+
+CB_EXPORT int cb_softcap(float* z, int n_rows, int width, float cap, void* stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    if (!(cap > 0.f) || n_rows > 65535) return CB_ERR_UNSUPPORTED;
+    cb_launch(softcap_kernel, dim3((width + 255) / 256, n_rows), dim3(256), 0, (cudaStream_t)stream, z, width,
+              cap, 1.0f / cap);
+    return cb_last_error();
+}
+
+// ---------------------------------------------------------------------------
 // Rotary encoding of q and k (half-split pairing) fused with the cache write.
 // qkv: [T, (Hq + 2 Hkv) * hd]; q is rotated in place; rotated k and plain v go
 // to the token's page: cache[page][kv_head][slot][feature].

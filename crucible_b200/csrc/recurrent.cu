@@ -14,6 +14,8 @@
 //                           (w a vector over the key channels, u a constant per head)
 //   state space, per token: S <- a S + (dt k) v^T;  o = S^T q + skip v
 //                           (a, dt numbers per head and token, skip a constant per head)
+//   retention, per token:   S <- decay S + k v^T;  o = S^T q   (decay a constant per head):
+//                           the state-space rule with a = decay, dt = 1 and no skip
 //
 // Kernels: the preparation of a step's rows (for the delta rule: a short causal
 // convolution over time per channel, whose last taps - 1 inputs are state too,
@@ -156,6 +158,53 @@ __global__ void mlstm_prepare_kernel(const T* __restrict__ proj, int proj_stride
         const float* g = gates + (size_t)t * gates_stride;
         log_in[(size_t)t * n_heads + h] = cap * tanhf((g[h] + bias_i[h]) / cap);
         log_keep[(size_t)t * n_heads + h] = logsigmoid_f(cap * tanhf((g[n_heads + h] + bias_f[h]) / cap));
+    }
+}
+
+// ---- retention: rotation of q and k, the keys' scale, the heads' fixed decays ---------------
+// proj row: [q: H*D | k: H*D | v: H*E | ...].  The first R features of every q and k head turn
+// by the fp32 angle position * freq[i], as split halves (i with i + R/2) or as neighbouring
+// pairs; k is multiplied by k_scale after the rotation; all of it fp32, written to qkv fp32
+// [rows][2*H*D + H*E].  keep[rows][H] receives the head's decay, step[rows][H] ones: what the
+// state-space rule of the recurrence reads per token.
+template <typename T>
+__global__ void retention_prepare_kernel(const T* __restrict__ proj, int proj_stride,
+                                         const float* __restrict__ freq, int rotary_dim, int split_halves,
+                                         const int* __restrict__ positions,
+                                         const float* __restrict__ head_decay, float k_scale,
+                                         float* __restrict__ qkv, float* __restrict__ keep,
+                                         float* __restrict__ step, int n_heads, int key_dim,
+                                         int value_dim) {
+    cb_pdl_trigger();
+    cb_pdl_wait();
+    const int t = blockIdx.x;
+    const int nq = n_heads * key_dim, C = 2 * nq + n_heads * value_dim;
+    const int half = rotary_dim >> 1;
+    const float pos = (float)positions[t];
+    const T* src = proj + (size_t)t * proj_stride;
+    float* dst = qkv + (size_t)t * C;
+    // the turning pairs of the 2H heads of q and k
+    for (int i = threadIdx.x; i < 2 * n_heads * half; i += blockDim.x) {
+        const int h = i / half, j = i - h * half;
+        const int ia = split_halves ? j : 2 * j, ib = split_halves ? j + half : 2 * j + 1;
+        float sn, cs;
+        sincosf(pos * freq[j], &sn, &cs);
+        const float a = cb_to_float(src[(size_t)h * key_dim + ia]), b = cb_to_float(src[(size_t)h * key_dim + ib]);
+        const float sc = h < n_heads ? 1.0f : k_scale;
+        dst[(size_t)h * key_dim + ia] = (a * cs - b * sn) * sc;
+        dst[(size_t)h * key_dim + ib] = (b * cs + a * sn) * sc;
+    }
+    // the features of q and k that pass unchanged
+    const int pass = key_dim - rotary_dim;
+    for (int i = threadIdx.x; i < 2 * n_heads * pass; i += blockDim.x) {
+        const int h = i / pass, f = rotary_dim + (i - h * pass);
+        const float x = cb_to_float(src[(size_t)h * key_dim + f]);
+        dst[(size_t)h * key_dim + f] = h < n_heads ? x : x * k_scale;
+    }
+    for (int c = 2 * nq + threadIdx.x; c < C; c += blockDim.x) dst[c] = cb_to_float(src[c]);
+    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
+        keep[(size_t)t * n_heads + h] = head_decay[h];
+        step[(size_t)t * n_heads + h] = 1.0f;
     }
 }
 
@@ -531,7 +580,8 @@ __global__ void gate_group_norm_kernel(const float* __restrict__ y, const T* __r
 }
 
 // ---- per-head RMS norm, gain and output gate ----------------------------------------------
-// o: fp32 [rows][H*E].  gain: [E] shared by the heads (gain_head_stride 0) or [H*E].
+// o: fp32 [rows][H*E].  gain: [E] shared by the heads (gain_head_stride 0) or [H*E], or null
+// (a norm without a weight).
 // gate: T rows (the joint projection) at a column offset.  out: T rows at a column offset.
 template <typename T, int GATE>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
@@ -550,11 +600,12 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
     const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)E + eps);
     const T* grow = gate + (size_t)t * gate_stride + (size_t)h * E;
     T* dst = out + (size_t)t * out_stride + (size_t)h * E;
-    const float* gn = gain + (size_t)h * gain_head_stride;
+    const float* gn = gain != nullptr ? gain + (size_t)h * gain_head_stride : nullptr;
     for (int e = lane; e < E; e += 32) {
         const float z = cb_to_float(grow[e]);
         const float gt = GATE == GATE_SILU ? silu_f(z) : sigmoid_f(z);
-        dst[e] = cb_from_float<T>(src[e] * r * gn[e] * gt * out_scale);
+        const float normed = gn != nullptr ? src[e] * r * gn[e] : src[e] * r;
+        dst[e] = cb_from_float<T>(normed * gt * out_scale);
     }
 }
 
@@ -664,6 +715,29 @@ CB_EXPORT int cb_mlstm_prepare(const void* proj, int proj_stride, int dtype, con
         cb_launch(mlstm_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)proj,
                   proj_stride, gates, gates_stride, bias_i, bias_f, cap, qkv, log_keep, log_in, n_heads,
                   key_dim, value_dim);
+    return cb_last_error();
+}
+
+// split_halves 0: neighbouring pairs turn, 1: feature i with i + rotary_dim / 2.
+CB_EXPORT int cb_retention_prepare(const void* proj, int proj_stride, int dtype, const float* freq,
+                                   int rotary_dim, int split_halves, const int* positions,
+                                   const float* head_decay, float k_scale, float* qkv, float* keep,
+                                   float* step, int n_rows, int n_heads, int key_dim, int value_dim,
+                                   void* stream) {
+    if (n_rows <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > key_dim || (rotary_dim & 1) || (rotary_dim && freq == nullptr))
+        return CB_ERR_UNSUPPORTED;
+    const int C = n_heads * (2 * key_dim + value_dim);
+    const dim3 grid(n_rows), block(C <= 512 ? 128 : (C >= 4096 ? 1024 : (C / 4 + 31) / 32 * 32));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CB_F32)
+        cb_launch(retention_prepare_kernel<float>, grid, block, 0, s, (const float*)proj, proj_stride, freq,
+                  rotary_dim, split_halves, positions, head_decay, k_scale, qkv, keep, step, n_heads,
+                  key_dim, value_dim);
+    else
+        cb_launch(retention_prepare_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)proj,
+                  proj_stride, freq, rotary_dim, split_halves, positions, head_decay, k_scale, qkv, keep,
+                  step, n_heads, key_dim, value_dim);
     return cb_last_error();
 }
 

@@ -25,7 +25,7 @@
 
 namespace {
 
-constexpr int MAX_PER_LANE = 8;   // key and value sizes <= 256
+// key and value sizes up to 32 * PER_LANE: 256 in the usual form, 1,024 in the wide one
 
 template <typename T>
 __global__ void rotate_norm_append_kernel(T* __restrict__ proj, int proj_stride,
@@ -90,6 +90,8 @@ __global__ void rotate_norm_append_kernel(T* __restrict__ proj, int proj_stride,
 // the first R features turn, as neighbouring pairs (2i, 2i + 1) or as split halves (i, i + R/2),
 // by the fp32 angle position * freq[i]; q stays in the row, k goes to the pages.  Values are
 // divided by their root mean square when value_eps >= 0 and copied as they are otherwise.
+// whole_norm: the root mean square is taken over ALL of the token's q features (and all of its
+// k features) at once instead of head by head, and the gains are [H * D] and [G * D].
 // Norms, angles and the rotation are fp32; one rounding to T at the end.
 template <typename T>
 __global__ void norm_rotate_append_kernel(T* __restrict__ proj, int proj_stride,
@@ -101,10 +103,11 @@ __global__ void norm_rotate_append_kernel(T* __restrict__ proj, int proj_stride,
                                           const int* __restrict__ block_table, int table_stride,
                                           T* __restrict__ k_cache, T* __restrict__ v_cache,
                                           int n_heads, int n_kv_heads, int key_dim, int value_dim,
-                                          int page_tokens, int write_cache, float value_eps) {
+                                          int page_tokens, int write_cache, float value_eps,
+                                          int whole_norm) {
     cb_pdl_trigger();
     cb_pdl_wait();
-    extern __shared__ float head_rows[];          // a row of key_dim floats per warp
+    extern __shared__ float head_rows[];          // a row of key_dim floats per warp, then 2 * warps sums
     const int t = blockIdx.x;
     T* row = proj + (size_t)t * proj_stride;
     const int pos = positions[t];
@@ -120,10 +123,42 @@ __global__ void norm_rotate_append_kernel(T* __restrict__ proj, int proj_stride,
     }
     float* mine = head_rows + (size_t)warp * key_dim;
     const int n_turn_heads = n_heads + (write_cache ? n_kv_heads : 0);
+    float r_q = 0.f, r_k = 0.f;
+    if (whole_norm) {
+        // the sums of squares over all q features and over all k features: every warp adds its
+        // share of both (the block's size is a function of the head counts alone, so a row's
+        // sum has one order whatever the step holds), then every thread adds the warps' shares
+        float* sums = head_rows + (size_t)n_warps * key_dim;
+        const int nq = n_heads * key_dim, nk = n_kv_heads * key_dim;
+        float sq = 0.f, sk = 0.f;
+        for (int f = threadIdx.x; f < nq; f += blockDim.x) {
+            const float x = cb_to_float(row[f]);
+            sq = fmaf(x, x, sq);
+        }
+        for (int f = threadIdx.x; f < nk; f += blockDim.x) {
+            const float x = cb_to_float(row[nq + f]);
+            sk = fmaf(x, x, sk);
+        }
+        sq = cb_warp_sum(sq);
+        sk = cb_warp_sum(sk);
+        if (lane == 0) {
+            sums[warp] = sq;
+            sums[n_warps + warp] = sk;
+        }
+        __syncthreads();
+        sq = sk = 0.f;
+        for (int w = 0; w < n_warps; ++w) {
+            sq += sums[w];
+            sk += sums[n_warps + w];
+        }
+        r_q = 1.0f / sqrtf(sq / (float)nq + qk_eps);
+        r_k = 1.0f / sqrtf(sk / (float)nk + qk_eps);
+    }
     for (int h = warp; h < n_turn_heads; h += n_warps) {
         const bool is_q = h < n_heads;
         T* src = row + (size_t)h * key_dim;
         const float* gain = is_q ? q_gain : k_gain;
+        if (whole_norm && gain != nullptr) gain += (size_t)(is_q ? h : h - n_heads) * key_dim;
         float ss = 0.f;
         for (int f = lane; f < key_dim; f += 32) {
             const float x = cb_to_float(src[f]);
@@ -131,7 +166,8 @@ __global__ void norm_rotate_append_kernel(T* __restrict__ proj, int proj_stride,
             ss = fmaf(x, x, ss);
         }
         if (gain != nullptr) {
-            const float r = 1.0f / sqrtf(cb_warp_sum(ss) / (float)key_dim + qk_eps);
+            const float r = whole_norm ? (is_q ? r_q : r_k)
+                                       : 1.0f / sqrtf(cb_warp_sum(ss) / (float)key_dim + qk_eps);
             for (int f = lane; f < key_dim; f += 32) mine[f] = mine[f] * r * gain[f];
         }
         __syncwarp();
@@ -166,14 +202,14 @@ __global__ void norm_rotate_append_kernel(T* __restrict__ proj, int proj_stride,
     }
 }
 
-template <typename T>
+template <typename T, int MAX_PER_LANE>
 __global__ void sink_attention_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ gate, int gate_stride,
     T* __restrict__ out, int out_stride, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
     const float* __restrict__ sinks, const int* __restrict__ positions,
     const int* __restrict__ row_request, const int* __restrict__ block_table, int table_stride,
     int n_rows, int n_heads, int n_kv_heads, int key_dim, int value_dim, int page_tokens,
-    float scale, int window, int keep_first, float out_scale) {
+    float scale, int window, int keep_first, float out_scale, int gate_per_head) {
     cb_pdl_trigger();
     cb_pdl_wait();
     const int warps_per_block = blockDim.x >> 5;
@@ -231,13 +267,14 @@ __global__ void sink_attention_kernel(
     }
     const float inv = corr / l;
     T* orow = out + (size_t)t * out_stride + (size_t)h * value_dim;
-    const T* grow = gate != nullptr ? gate + (size_t)t * gate_stride + (size_t)h * value_dim : nullptr;
+    const T* grow = gate != nullptr
+        ? gate + (size_t)t * gate_stride + (gate_per_head ? (size_t)h : (size_t)h * value_dim) : nullptr;
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
         const int f = lane + 32 * i;
         if (f < value_dim) {
             float o = acc[i] * inv;
-            if (grow != nullptr) o *= 1.0f / (1.0f + expf(-cb_to_float(grow[f])));
+            if (grow != nullptr) o *= 1.0f / (1.0f + expf(-cb_to_float(grow[gate_per_head ? 0 : f])));
             orow[f] = cb_from_float<T>(o * out_scale);
         }
     }
@@ -271,32 +308,33 @@ CB_EXPORT int cb_rotate_norm_append(void* proj, int proj_stride, int dtype, cons
 
 // The general preparation (see norm_rotate_append_kernel): q_gain / k_gain null: no norm of
 // q and k; split_halves 0: neighbouring pairs turn, 1: feature i with i + rotary_dim / 2;
-// value_eps < 0: values are cached as they are.
+// value_eps < 0: values are cached as they are; whole_norm 1: one root mean square over all of
+// a token's q features (and one over its k features), gains [H * D] and [G * D].
 CB_EXPORT int cb_norm_rotate_append(void* proj, int proj_stride, int dtype, const float* q_gain,
                                     const float* k_gain, float qk_eps, const float* freq,
                                     int rotary_dim, int split_halves, const int* positions,
                                     const int* row_request, const int* block_table, int table_stride,
                                     void* k_cache, void* v_cache, int n_rows, int n_heads,
                                     int n_kv_heads, int key_dim, int value_dim, int page_tokens,
-                                    int write_cache, float value_eps, void* stream) {
+                                    int write_cache, float value_eps, int whole_norm, void* stream) {
     if (n_rows <= 0) return 0;
     if (rotary_dim < 0 || rotary_dim > key_dim || (rotary_dim & 1) || key_dim > 4096) return CB_ERR_UNSUPPORTED;
     int warps = n_heads + n_kv_heads;
     warps = warps > 8 ? 8 : warps;
-    const size_t smem = (size_t)warps * key_dim * sizeof(float);
+    const size_t smem = ((size_t)warps * key_dim + 2 * warps) * sizeof(float);
     if (smem > 48 * 1024) return CB_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
         cb_launch(norm_rotate_append_kernel<float>, dim3(n_rows), dim3(warps * 32), smem, s, (float*)proj,
                   proj_stride, q_gain, k_gain, qk_eps, freq, rotary_dim, split_halves, positions,
                   row_request, block_table, table_stride, (float*)k_cache, (float*)v_cache, n_heads,
-                  n_kv_heads, key_dim, value_dim, page_tokens, write_cache, value_eps);
+                  n_kv_heads, key_dim, value_dim, page_tokens, write_cache, value_eps, whole_norm);
     else
         cb_launch(norm_rotate_append_kernel<__nv_bfloat16>, dim3(n_rows), dim3(warps * 32), smem, s,
                   (__nv_bfloat16*)proj, proj_stride, q_gain, k_gain, qk_eps, freq, rotary_dim,
                   split_halves, positions, row_request, block_table, table_stride,
                   (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, n_heads, n_kv_heads, key_dim,
-                  value_dim, page_tokens, write_cache, value_eps);
+                  value_dim, page_tokens, write_cache, value_eps, whole_norm);
     return cb_last_error();
 }
 
@@ -306,26 +344,26 @@ CB_EXPORT int cb_sink_attention(const void* q, int q_stride, const void* gate, i
                                 const int* row_request, const int* block_table, int table_stride,
                                 int n_rows, int n_heads, int n_kv_heads, int key_dim, int value_dim,
                                 int page_tokens, float scale, int window, int keep_first,
-                                float out_scale, void* stream) {
+                                float out_scale, int gate_per_head, void* stream) {
     if (n_rows <= 0) return 0;
-    if (key_dim > 32 * MAX_PER_LANE || value_dim > 32 * MAX_PER_LANE || n_heads % n_kv_heads != 0)
-        return CB_ERR_UNSUPPORTED;
+    if (key_dim > 1024 || value_dim > 1024 || n_heads % n_kv_heads != 0) return CB_ERR_UNSUPPORTED;
+    const bool wide = key_dim > 256 || value_dim > 256;
     const int warps = 4;
     const long units = (long)n_rows * n_heads;
     const int blocks = (int)((units + warps - 1) / warps);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == CB_F32)
-        cb_launch(sink_attention_kernel<float>, dim3(blocks), dim3(warps * 32), 0, s, (const float*)q,
-                  q_stride, (const float*)gate, gate_stride, (float*)out, out_stride,
-                  (const float*)k_cache, (const float*)v_cache, sinks, positions, row_request,
-                  block_table, table_stride, n_rows, n_heads, n_kv_heads, key_dim, value_dim,
-                  page_tokens, scale, window, keep_first, out_scale);
-    else
-        cb_launch(sink_attention_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, s,
-                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride,
-                  (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache,
-                  (const __nv_bfloat16*)v_cache, sinks, positions, row_request, block_table,
-                  table_stride, n_rows, n_heads, n_kv_heads, key_dim, value_dim, page_tokens, scale,
-                  window, keep_first, out_scale);
+#define CB_SINK_LAUNCH(TT, PL)                                                                          \
+    cb_launch(sink_attention_kernel<TT, PL>, dim3(blocks), dim3(warps * 32), 0, s, (const TT*)q, q_stride, \
+              (const TT*)gate, gate_stride, (TT*)out, out_stride, (const TT*)k_cache, (const TT*)v_cache, \
+              sinks, positions, row_request, block_table, table_stride, n_rows, n_heads, n_kv_heads,    \
+              key_dim, value_dim, page_tokens, scale, window, keep_first, out_scale, gate_per_head)
+    if (dtype == CB_F32) {
+        if (wide) CB_SINK_LAUNCH(float, 32);
+        else CB_SINK_LAUNCH(float, 8);
+    } else {
+        if (wide) CB_SINK_LAUNCH(__nv_bfloat16, 32);
+        else CB_SINK_LAUNCH(__nv_bfloat16, 8);
+    }
+#undef CB_SINK_LAUNCH
     return cb_last_error();
 }

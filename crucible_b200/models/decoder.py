@@ -28,7 +28,8 @@ from ..parts import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NOR
 class CacheGroupSpec:
     """Layers whose keys and values share pages: one pool, one block table."""
     need: CacheNeed
-    layers: Tuple[int, ...]          # stored-layer indices, in slot order
+    layers: Tuple[int, ...]          # stored-layer indices, in slot order (a layer that runs in
+                                     # several copies has a slot for each)
 
 
 @dataclass(frozen=True)
@@ -36,6 +37,26 @@ class TensorRequest:
     key: str                         # "<part path>.<local name>", unique in the model
     checkpoint_name: str
     decl: TensorDecl
+
+
+class ModelVectors:
+    """Tables of the model itself: float32 rows as wide as the model, by name.  A run-order
+    entry may add one of their rows to the residual before its layer runs."""
+
+    def __init__(self, tables, width: int):
+        self.tables = tuple(tables)
+        self.width = width
+        self.bound: Dict[str, torch.Tensor] = {}
+
+    def tensors(self):
+        return [TensorDecl(name, (rows, self.width), role="vector", init=("normal", 0.0, 0.5))
+                for name, rows in self.tables]
+
+    def bind(self, tensors, dtype, device):
+        self.bound = {name: tensors[name].contiguous() for name, _ in self.tables}
+
+    def row(self, name: str, index: int) -> torch.Tensor:
+        return self.bound[name][index]
 
 
 class DecoderModel:
@@ -46,6 +67,7 @@ class DecoderModel:
         self.head = HEADS.build(config.head.kind, config.head, config.vocab_size,
                                 config.hidden_size, config.tie_word_embeddings)
         self.final_norm = NORMS.build(config.final_norm.kind, config.final_norm)
+        self.vectors = ModelVectors(config.vectors, config.hidden_size)
         self.layers = []
         for spec in config.layers:
             mixer = MIXERS.build(spec.mixer.kind, spec.mixer)
@@ -60,24 +82,25 @@ class DecoderModel:
 
     def _plan_storage(self):
         """Cache groups, one binding per run-order entry, state bytes per request."""
-        owners: Dict[int, Tuple[int, int]] = {}       # stored layer -> (group, slot)
+        owners: Dict[Tuple[int, int], Tuple[int, int]] = {}   # (stored layer, copy) -> (group, slot)
         groups: List[Tuple[CacheNeed, List[int]]] = []
-        # a layer that only ever runs on another layer's cache gets no pages of its own
-        runs_on_own = {e.layer for e in self.config.run_order if e.cache_of is None}
-        for li, layer in enumerate(self.layers):
-            need = layer.mixer.cache_need()
-            if need is None or li not in runs_on_own:
+        # a layer that only ever runs on another layer's cache gets no pages of its own; a
+        # layer that runs in several copies gets a slot for each
+        runs_on_own = sorted({(e.layer, e.copy) for e in self.config.run_order if e.cache_of is None})
+        for li, copy in runs_on_own:
+            need = self.layers[li].mixer.cache_need()
+            if need is None:
                 continue
             for gi, (gneed, members) in enumerate(groups):
                 if gneed == need:
-                    owners[li] = (gi, len(members))
+                    owners[(li, copy)] = (gi, len(members))
                     members.append(li)
                     break
             else:
-                owners[li] = (len(groups), 0)
+                owners[(li, copy)] = (len(groups), 0)
                 groups.append((need, [li]))
         bindings: List[LayerBinding] = []
-        state_offsets: Dict[int, int] = {}
+        state_offsets: Dict[Tuple[int, int], int] = {}
         total_state = 0
         # an embedding that remembers something of a request between steps (its last token,
         # say) keeps it at the head of the request's state slot
@@ -85,37 +108,42 @@ class DecoderModel:
         if nbytes:
             self.embedding.state_binding = LayerBinding(state_offset=0, state_bytes=nbytes)
             total_state = (nbytes + 15) // 16 * 16
-        written = set()
+        written, ran = set(), set()
         for i, entry in enumerate(self.config.run_order):
             layer = self.layers[entry.layer]
             nbytes = int(layer.mixer.state_bytes())
-            if nbytes and entry.layer not in state_offsets:
-                state_offsets[entry.layer] = total_state
+            me = (entry.layer, entry.copy)
+            if nbytes and me not in state_offsets:
+                state_offsets[me] = total_state
                 total_state += (nbytes + 15) // 16 * 16
             group = slot = None
             write = True
             if entry.cache_of is not None:
-                src = entry.cache_of
+                src = (entry.cache_of, entry.copy)
                 if src not in owners:
-                    raise ConfigError(f"run_order[{i}] reads the cache of layer {src}, "
+                    raise ConfigError(f"run_order[{i}] reads the cache of layer {src[0]}, "
                                       f"whose mixer keeps none")
-                if layer.mixer.cache_need() != self.layers[src].mixer.cache_need():
+                if layer.mixer.cache_need() != self.layers[src[0]].mixer.cache_need():
                     raise ConfigError(f"run_order[{i}]: layer {entry.layer} cannot read the "
-                                      f"cache of layer {src}: their cache needs differ")
+                                      f"cache of layer {src[0]}: their cache needs differ")
                 if src not in written:
-                    raise ConfigError(f"run_order[{i}] reads the cache of layer {src} "
+                    raise ConfigError(f"run_order[{i}] reads the cache of layer {src[0]} "
                                       f"before that layer has run")
                 group, slot = owners[src]
                 write = False
-            elif entry.layer in owners:
-                group, slot = owners[entry.layer]
-                if entry.layer in written:
+            elif me in owners:
+                group, slot = owners[me]
+                if me in written:
                     raise ConfigError(f"run_order[{i}] runs layer {entry.layer} a second "
                                       f"time and would write its cache twice; name "
-                                      f"cache_of to read it instead")
-                written.add(entry.layer)
+                                      f"cache_of to read it instead, or another copy")
+                written.add(me)
+            elif nbytes and me in ran:
+                raise ConfigError(f"run_order[{i}] runs layer {entry.layer} a second time on "
+                                  f"the same state; name another copy")
+            ran.add(me)
             bindings.append(LayerBinding(group=group, slot=slot or 0, write=write,
-                                         state_offset=state_offsets.get(entry.layer, 0),
+                                         state_offset=state_offsets.get(me, 0),
                                          state_bytes=nbytes))
         specs = [CacheGroupSpec(need, tuple(members)) for need, members in groups]
         return specs, bindings, total_state
@@ -127,6 +155,8 @@ class DecoderModel:
         yield "embedding", self.embedding, None
         yield "head", self.head, None
         yield "final_norm", self.final_norm, None
+        if self.vectors.tables:
+            yield "vectors", self.vectors, None
         for li, layer in enumerate(self.layers):
             for name, norm in layer.norms.items():
                 yield f"layer.{name}", norm, li
@@ -193,7 +223,11 @@ class DecoderModel:
             # the norm that reads the rows after this layer, for the layer's last product
             nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
             entry_norm = getattr(nxt, "entry_norm", None)
-            ctx.norm_after_layer = entry_norm() if entry_norm is not None else None
+            # (rows that get a vector added before the next layer are not final when this one ends)
+            ctx.norm_after_layer = (entry_norm() if entry_norm is not None and order[i + 1].add is None
+                                    else None)
+            if entry.add is not None:
+                ops.add_vector(x, self.vectors.row(*entry.add))
             self.layers[entry.layer].forward(ctx, x, binding)
         ctx.norm_after_layer = None
         if ctx.n_logit_rows == 0:

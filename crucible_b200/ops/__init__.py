@@ -227,6 +227,29 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
                               _c_int(x.shape[1]), _stream()), "gather_rows")
 
 
+def add_vector(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[t, :] += v for every row of the float32 residual."""
+    _need_cuda(x, v)
+    if (x.dtype != torch.float32 or v.dtype != torch.float32 or x.dim() != 2 or v.dim() != 1
+            or v.shape[0] != x.shape[1]):
+        raise KernelError("add_vector takes float32 rows [T, W] and a float32 vector [W]")
+    _contig(x, "add_vector rows"); _contig(v, "add_vector vector")
+    lib = build.load("elementwise")
+    _check(lib.cb_add_vector(_ptr(x), _ptr(v), _c_int(x.shape[0]), _c_int(x.shape[1]), _stream()),
+           "add_vector")
+
+
+def softcap(z: torch.Tensor, cap: float) -> None:
+    """z <- cap * tanh(z / cap) in place, float32 rows."""
+    _need_cuda(z)
+    if z.dtype != torch.float32 or z.dim() != 2:
+        raise KernelError("softcap takes float32 rows")
+    _contig(z, "softcap rows")
+    lib = build.load("elementwise")
+    _check(lib.cb_softcap(_ptr(z), _c_int(z.shape[0]), _c_int(z.shape[1]), _c_float(cap), _stream()),
+           "softcap")
+
+
 # ---------------------------------------------------------------------------
 # matrix products: out[M, N] (+)= a[M, K] . w[N, K]^T
 # ---------------------------------------------------------------------------

@@ -55,6 +55,30 @@ def mlstm_prepare(proj, gates, bias_i, bias_f, cap, qkv, log_keep, log_in, n_hea
         _c_int(n_heads), _c_int(key_dim), _c_int(value_dim), _stream()), "mlstm_prepare")
 
 
+def retention_prepare(proj, freq, rotary_dim: int, split_halves: bool, ctx, head_decay, k_scale: float,
+                      qkv, keep, step, n_heads: int, key_dim: int, value_dim: int) -> None:
+    """Rows of `proj` are [q: H*D | k: H*D | v: H*E | ...]: the first `rotary_dim` features of
+    every q and k head turn by position * freq (float32), k times `k_scale` afterwards; qkv =
+    float32 [q | k | v]; keep[t, h] = head_decay[h], step[t, h] = 1 (what the state-space rule
+    of `matrix_memory` reads for S <- decay S + k v^T)."""
+    _need_cuda(proj, freq, head_decay, qkv, keep, step)
+    if (proj.stride(1) != 1 or qkv.dtype != torch.float32 or not qkv.is_contiguous()
+            or qkv.shape[1] != n_heads * (2 * key_dim + value_dim)
+            or head_decay.dtype != torch.float32 or head_decay.numel() != n_heads
+            or keep.dtype != torch.float32 or step.dtype != torch.float32
+            or not keep.is_contiguous() or not step.is_contiguous()):
+        raise KernelError("retention_prepare: contiguous rows, float32 outputs [rows, H (2D + E)] and "
+                          "[rows, H], one float32 decay per head")
+    if rotary_dim and (freq is None or freq.dtype != torch.float32 or freq.numel() * 2 != rotary_dim):
+        raise KernelError("retention_prepare: freq is float32 [rotary_dim / 2]")
+    lib = build.load("recurrent")
+    _check(lib.cb_retention_prepare(
+        _ptr(proj), _c_int(proj.stride(0)), _c_int(_code(proj.dtype)), _ptr(freq), _c_int(rotary_dim),
+        _c_int(1 if split_halves else 0), _ptr(ctx.positions), _ptr(head_decay), _c_float(k_scale),
+        _ptr(qkv), _ptr(keep), _ptr(step), _c_int(proj.shape[0]), _c_int(n_heads), _c_int(key_dim),
+        _c_int(value_dim), _stream()), "retention_prepare")
+
+
 def matrix_memory(rule, qkv, q_off, k_off, v_off, sc0, sc1, ctx, state, s_off, n_off, m_off, out,
                   n_heads, n_qk_heads, key_dim, value_dim, w_off=0, per_head=None) -> None:
     """Walks every request's tokens in order through its heads' matrices (see the kernel).
@@ -78,7 +102,7 @@ def matrix_memory(rule, qkv, q_off, k_off, v_off, sc0, sc1, ctx, state, s_off, n
 def head_norm_gate(o, gain, gain_per_head, gate, out, gate_kind, n_heads, value_dim, eps,
                    out_scale) -> None:
     """out = o / rms(o over a head) * gain * act(gate) * out_scale; `gate` and `out` are
-    views of rows in the engine dtype."""
+    views of rows in the engine dtype.  `gain` None: a norm without a weight."""
     _need_cuda(o, gain, gate, out)
     if o.dtype != torch.float32 or gate.dtype != out.dtype or gate.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("head_norm_gate: float32 input, gate and output rows of one dtype")

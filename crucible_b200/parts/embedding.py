@@ -112,11 +112,16 @@ class HashedPositionEmbedding(Embedding):
 
 
 class LMHead(Head):
-    def __init__(self, vocab_size: int, width: int, tied: bool):
+    """logits = rows W^T; option `softcap` (a positive number c): logits <- c tanh(logits / c)."""
+
+    def __init__(self, vocab_size: int, width: int, tied: bool, softcap=None):
         self.vocab_size = vocab_size
         self.width = width
         self.tied = tied
         self.weight = None
+        self.softcap = float(softcap) if softcap else None
+        if self.softcap is not None and not self.softcap > 0:
+            raise ValueError(f"the head's soft cap must be positive, got {softcap!r}")
 
     def tensors(self):
         return [] if self.tied else [TensorDecl("weight", (self.vocab_size, self.width))]
@@ -132,10 +137,12 @@ class LMHead(Head):
     def forward(self, ctx, normed_rows: torch.Tensor) -> torch.Tensor:
         logits = ctx.scratch("logits", (normed_rows.shape[0], self.vocab_size), torch.float32)
         ops.linear(normed_rows, self.weight, logits)
+        if self.softcap is not None:
+            ops.softcap(logits, self.softcap)
         return logits
 
 
 EMBEDDINGS.register("token", lambda spec, vocab, width: TokenEmbedding(vocab, width))
 EMBEDDINGS.register("token_normed_streams", NormedStreamsEmbedding)
 EMBEDDINGS.register("token_hashed_positions", HashedPositionEmbedding)
-HEADS.register("linear", lambda spec, vocab, width, tied: LMHead(vocab, width, tied))
+HEADS.register("linear", lambda spec, vocab, width, tied: LMHead(vocab, width, tied, spec.option("softcap")))

@@ -14,6 +14,8 @@ Options of the spec (beside heads, head_dim, softmax_scale, window, position):
   gate        True or "head": the head's output times sigmoid(h Wg^T)_i, one logit a head
               (`g` [heads, width], logits in float32); "element": the concatenated heads times
               sigmoid(h Wg^T) feature by feature (`g` [heads * value_dim, width]); False: none;
+  sink        True: a learned number per head (`sink` [heads]) joins the softmax's denominator
+              as exp(sink), with no key and no value, unscaled;
   reads_other True: the layer has no Wdkv; it reads the rows another layer left in the pages
               (the run order names that layer: `RunEntry.cache_of`) with its own W_uk, W_uv,
               queries and window;
@@ -53,6 +55,7 @@ class LatentAttention(Mixer):
         self.gate = {True: "head", False: None, None: None}.get(gate, gate)
         self.q_rank = s.option("q_rank")
         self.reads_other = bool(s.option("reads_other", False))
+        self.has_sink = bool(s.option("sink", False))
         if self.H <= 0 or self.D <= 0 or self.E <= 0 or self.C <= 0 or self.R < 0 or self.R % 2:
             raise ValueError("latent attention: positive heads, dim, vdim and kv_rank; an even rot_dim")
         if self.gate not in (None, "head", "element"):
@@ -89,6 +92,8 @@ class LatentAttention(Mixer):
             out.append(TensorDecl("g", (H, d)))
         elif self.gate == "element":
             out.append(TensorDecl("g", (H * E, d)))
+        if self.has_sink:
+            out.append(TensorDecl("sink", (H,), role="vector", init=("normal", 0.0, 1.0)))
         return out
 
     def bind(self, tensors, dtype, device):
@@ -114,6 +119,7 @@ class LatentAttention(Mixer):
         self.uk_t = tensors["uk"].view(H, D, C).transpose(1, 2).contiguous()
         self.uv = tensors["uv"].view(H, E, C).contiguous()
         self.w_out = tensors["o"]
+        self.sinks = tensors.get("sink") if self.has_sink else None
         self.dtype = dtype
         ops.declare_weights(self.w_in, self.w_gate, self.uk_t, self.uv, self.w_out, self.w_dq, self.w_uq)
         if self.position is not None:
@@ -154,7 +160,14 @@ class LatentAttention(Mixer):
                         binding, split_halves=split)
         kernels.heads_linear(q, D + R, self.uk_t, qx, row)
         ox = ctx.scratch("latent.ox", (t, H * row), self.dtype)
-        ops.paged_attention(qx, ox, H, 1, row, self.spec.softmax_scale, self.spec.window, ctx, cache, binding)
+        if self.sinks is not None:
+            # the softmax with one more term in its denominator: the attention that has a sink,
+            # over the same ONE key head whose rows are keys and values at once
+            from ..ops import sink_attention
+            sink_attention.attention(qx, None, ox, self.sinks, H, 1, row, row, self.spec.softmax_scale,
+                                     self.spec.window, 0, 1.0, ctx, cache, binding)
+        else:
+            ops.paged_attention(qx, ox, H, 1, row, self.spec.softmax_scale, self.spec.window, ctx, cache, binding)
         act = ctx.scratch("latent.act", (t, H * E), self.dtype)
         logit = gate_rows = None
         if self.w_gate is not None:

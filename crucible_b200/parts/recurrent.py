@@ -30,6 +30,13 @@ SiLU; dt = softplus(dt + dt_bias).  Per head (head i uses group i // (H / G)):
     S <- exp(-exp(A_log) dt) S + dt B x^T;   y = S^T C + D x.
 y * silu(z), then unit rms in `norm_groups` equal parts of the row, times norm [H * P], goes
 through Wo.
+
+`retention` (linear attention with a fixed decay per head, no softmax and no denominator):
+q, k [H, D], v [H, E]; q and k turn by the spec's position encoding (the first rotary_dim
+features of each head), k times D^-1/2 after the rotation.  Per head, with the constant
+decay_h of the spec's option `decay`:
+    S <- decay_h S + k v^T;   o = S^T q.
+o / rms(o) per head (no weight), times silu(h Wg^T), goes through Wo.
 """
 from __future__ import annotations
 
@@ -38,7 +45,7 @@ import torch
 from ..config.model_config import MixerSpec
 from ..ops import recurrent as kernels
 from .. import ops
-from .base import MIXERS, Mixer, TensorDecl
+from .base import MIXERS, POSITIONS, Mixer, TensorDecl
 from .branch import BranchMixer
 
 
@@ -281,7 +288,64 @@ class StateSpaceMixer(BranchMixer):
         kernels.gate_group_norm(y, proj[:, :inner], self.gain, act, self.parts, self.eps)
 
 
+class Retention(BranchMixer):
+    def __init__(self, spec: MixerSpec):
+        s = self.spec = spec
+        self.H, self.D = s.n_heads, s.head_dim
+        self.E = int(s.option("value_dim", s.head_dim))
+        self.eps = float(s.option("norm_eps", 1e-6))
+        self.decay_values = tuple(float(x) for x in (s.option("decay") or ()))
+        if self.H <= 0 or self.D <= 0 or self.E <= 0:
+            raise ValueError("retention: heads and sizes must be positive")
+        if self.D > 256:
+            raise ValueError("retention: key size up to 256")
+        if len(self.decay_values) != self.H or not all(0.0 <= x <= 1.0 for x in self.decay_values):
+            raise ValueError("retention: one decay in [0, 1] for every head")
+        self.position = POSITIONS.build(s.position.kind, s.position) if s.position is not None else None
+        if self.position is not None and not hasattr(self.position, "frequencies"):
+            raise ValueError("retention: the position encoding must give `frequencies()`")
+        self.s_bytes = _round16(4 * self.H * self.D * self.E)
+
+    def tensors(self):
+        d, H, D, E = self.spec.width, self.H, self.D, self.E
+        return [TensorDecl("q", (H * D, d)), TensorDecl("k", (H * D, d)), TensorDecl("v", (H * E, d)),
+                TensorDecl("g", (H * E, d)), TensorDecl("o", (d, H * E))]
+
+    def bind(self, tensors, dtype, device):
+        self.w_in = torch.cat([tensors["q"], tensors["k"], tensors["v"], tensors["g"]], 0).contiguous()
+        self.w_out = tensors["o"]
+        # the decays are numbers of the configuration: float32 as they are; the state-space
+        # rule's skip is zero here
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=device)
+        self.no_skip = torch.zeros(self.H, dtype=torch.float32, device=device)
+        self.dtype = dtype
+        self._declare()
+        if self.position is not None:
+            self.position.bind({}, dtype, device)
+
+    def state_bytes(self) -> int:
+        return self.s_bytes
+
+    def run_branch(self, ctx, proj, gates, act, out_scale, binding):
+        t, H, D, E = proj.shape[0], self.H, self.D, self.E
+        C = 2 * H * D + H * E
+        state = ctx.state(binding)
+        qkv = ctx.scratch("retention.qkv", (t, C), torch.float32)
+        keep = ctx.scratch("retention.keep", (t, H), torch.float32)
+        step = ctx.scratch("retention.step", (t, H), torch.float32)
+        o = ctx.scratch("retention.o", (t, H * E), torch.float32)
+        freq, rotary_dim = self.position.frequencies() if self.position is not None else (None, 0)
+        split = bool(getattr(self.position, "split_halves", True))
+        kernels.retention_prepare(proj, freq, rotary_dim, split, ctx, self.decay, float(D) ** -0.5, qkv,
+                                  keep, step, H, D, E)
+        kernels.matrix_memory(kernels.SSD, qkv, 0, H * D, 2 * H * D, keep, step, ctx, state, 0, 0, 0, o,
+                              H, H, D, E, per_head=self.no_skip)
+        kernels.head_norm_gate(o, None, False, proj[:, C:C + H * E], act, kernels.GATE_SILU, H, E,
+                               self.eps, out_scale)
+
+
 MIXERS.register("gated_delta", GatedDeltaRule)
+MIXERS.register("retention", Retention)
 MIXERS.register("wkv", WKVMixer)
 MIXERS.register("mamba2", StateSpaceMixer)
 MIXERS.register("mlstm", MLSTM)

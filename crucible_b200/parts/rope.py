@@ -69,7 +69,8 @@ class InterleavedRotary(PositionEncoding):
 
     def bind(self, tensors, dtype, device):
         n = self.spec.rotary_dim
-        i = torch.arange(n // 2, dtype=torch.float32)
+        i = torch.arange(n // 2, dtype=torch.float64)
+        # taken in float64 and rounded once, so every frequency is the nearest float32
         self.freq = (float(self.spec.theta) ** (-2.0 * i / n)).to(torch.float32).to(device) if n else None
 
     def frequencies(self):

@@ -12,9 +12,13 @@ scaled.  The heads' results times sigmoid(h Wg^T) go through Wo.
 
 Options of the spec: value_dim (default head_dim), keep_first (default 0), sink
 (default true), value_norm_eps (None: values are cached as they are), gate (default
-true), qk_norm_eps (default None; a number: every q and k head is divided by its root mean
-square over D, that eps under the root, and multiplied by the weight `q.norm` / `k.norm` of
-size D that all heads share, before the rotation).  `window` None means every earlier key.
+true or "element": a logit for every output feature, `g` [H * E, width]; "head": one logit a
+head, `g` [H, width]; false: none), qk_norm_eps (default None; a number: every q and k head is
+divided by its root mean square over D, that eps under the root, and multiplied by the weight
+`q.norm` / `k.norm` of size D that all heads share, before the rotation), qk_norm_whole
+(default false; true: the root mean square is taken over the whole projection, all H * D
+features of q at once and all G * D of k, and the weights have those sizes).  `window` None
+means every earlier key.
 The position encoding says which features pair (`split_halves`: i with i + R/2, else
 neighbours).
 """
@@ -41,7 +45,12 @@ class SinkWindowAttention(BranchMixer):
         self.value_dim = int(spec.option("value_dim", spec.head_dim))
         self.keep_first = int(spec.option("keep_first", 0))
         self.has_sink = bool(spec.option("sink", True))
-        self.has_gate = bool(spec.option("gate", True))
+        gate = spec.option("gate", True)
+        self.gate = {True: "element", False: None, None: None}.get(gate, gate)
+        if self.gate not in (None, "element", "head"):
+            raise ValueError(f"attention: gate is 'element', 'head' or none, got {gate!r}")
+        self.has_gate = self.gate is not None
+        self.qk_whole = bool(spec.option("qk_norm_whole", False))
         self.value_eps = spec.option("value_norm_eps")
         self.qk_eps = spec.option("qk_norm_eps")
         if self.keep_first < 0 or self.value_dim <= 0:
@@ -59,12 +68,13 @@ class SinkWindowAttention(BranchMixer):
                TensorDecl("v", (s.n_kv_heads * self.value_dim, d)),
                TensorDecl("o", (d, s.n_heads * self.value_dim))]
         if self.has_gate:
-            out.append(TensorDecl("g", (s.n_heads * self.value_dim, d)))
+            out.append(TensorDecl("g", (s.n_heads * (self.value_dim if self.gate == "element" else 1), d)))
         if self.has_sink:
             out.append(TensorDecl("sink", (s.n_heads,), role="vector", init=("normal", 0.0, 1.0)))
         if self.qk_eps is not None:
-            out += [TensorDecl("q.norm", (s.head_dim,), role="vector", init=("normal", 1.0, 0.1)),
-                    TensorDecl("k.norm", (s.head_dim,), role="vector", init=("normal", 1.0, 0.1))]
+            nq, nk = (s.n_heads, s.n_kv_heads) if self.qk_whole else (1, 1)
+            out += [TensorDecl("q.norm", (nq * s.head_dim,), role="vector", init=("normal", 1.0, 0.1)),
+                    TensorDecl("k.norm", (nk * s.head_dim,), role="vector", init=("normal", 1.0, 0.1))]
         return out
 
     def bind(self, tensors, dtype, device):
@@ -97,13 +107,16 @@ class SinkWindowAttention(BranchMixer):
             kernels.norm_rotate_append(proj, self.q_gain, self.k_gain,
                                        float(self.qk_eps) if self.qk_eps is not None else 0.0, freq,
                                        rotary_dim, split, s.n_heads, s.n_kv_heads, s.head_dim,
-                                       self.value_dim, self.value_eps, ctx, cache, binding)
+                                       self.value_dim, self.value_eps, ctx, cache, binding,
+                                       whole_norm=self.qk_whole and self.qk_eps is not None)
         q_width = s.n_heads * s.head_dim
         g_at = q_width + s.n_kv_heads * (s.head_dim + self.value_dim)
-        gate = proj[:, g_at:g_at + s.n_heads * self.value_dim] if self.has_gate else None
+        per_head = self.gate == "head"
+        gate = (proj[:, g_at:g_at + s.n_heads * (1 if per_head else self.value_dim)]
+                if self.has_gate else None)
         kernels.attention(proj[:, :q_width], gate, act, self.sinks, s.n_heads, s.n_kv_heads,
                           s.head_dim, self.value_dim, s.softmax_scale, s.window, self.keep_first,
-                          out_scale, ctx, cache, binding)
+                          out_scale, ctx, cache, binding, gate_per_head=per_head)
 
 
 MIXERS.register("sink_attention", SinkWindowAttention)
