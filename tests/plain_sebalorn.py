@@ -225,3 +225,12 @@ def load_folder(path):
             raise ValueError(f"{name}: dtype {meta['dtype']}")
         out[name] = t.reshape(meta["shape"])
     return config, out
+
+
+def greedy(config, w, prompt, n, dtype=torch.float64):
+    """`n` tokens after `prompt`, each the largest logit (the lowest index on ties); the whole
+    sequence is run again for every token."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(torch.argmax(forward(config, w, tokens, dtype)[-1])))
+    return tokens[len(prompt):]
