@@ -621,16 +621,17 @@ def run_profile_case(args):
 
 
 def run_design_comparison(args):
-    """`--compare vuvosun` / `--compare futepel` / `--compare nipapel`: prefill and decode throughput of that design at
+    """`--compare vuvosun` / `--compare futepel` / `--compare nipapel` / `--compare sebalorn`: prefill and decode throughput of that design at
     a few sizes of a real model's proportions (random weights), beside the dense Llama-style
     decoder (and, for futepel, beside Vuvosun, the nearest design with recurrent mixers; for nipapel,
-    beside Futepel, the nearest design with a latent attention and experts) at
+    beside Futepel, the nearest design with a latent attention and experts; for sebalorn, beside Nipapel,
+    the nearest design with one norm a layer and both attentions, and Vuvosun, the nearest with a matrix memory) at
     equal width, layers, heads, feed-forward width and vocabulary; and, from one eager prompt
     step and one eager decode step each, the device time of every kind of launch."""
     import torch
     from crucible_b200 import ops
     from crucible_b200.config import parse_config
-    from crucible_b200.config.presets import COMPARISON_SIZES, _llama, futepel, nipapel, vuvosun
+    from crucible_b200.config.presets import COMPARISON_SIZES, _llama, futepel, nipapel, sebalorn, vuvosun
     from crucible_b200.engine import Engine, EngineOptions, StepEntry
     from crucible_b200.weights import write_random_model
     peaks = read_peaks()
@@ -647,6 +648,10 @@ def run_design_comparison(args):
         if args.compare == "nipapel":
             raws = {"nipapel": nipapel(width, heads, kv, hd, ff, vocab, layers=layers),
                     "futepel": futepel(width, heads, kv, hd, ff, vocab, layers=layers), "llama": raws["llama"]}
+        if args.compare == "sebalorn":
+            raws = {"sebalorn": sebalorn(width, heads, kv, hd, ff, vocab, layers=layers),
+                    "nipapel": nipapel(width, heads, kv, hd, ff, vocab, layers=layers),
+                    "vuvosun": raws["vuvosun"], "llama": raws["llama"]}
         row = {}
         for design, raw in raws.items():
             pages = (batch + 1) * (-(-(ctx_len + args.steps + args.warmup + 64) // 16)) + 256
@@ -715,14 +720,14 @@ def main():
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=2048)
     p.add_argument("--shape", default="120m", choices=sorted(SHAPE_LABEL) + ["vuvosun-w1024", "vuvosun-w2048", "futepel-w1024", "futepel-w2048",
-                                                                      "nipapel-w1024", "nipapel-w2048"],
-                   help="a named shape; the default is the benchmark's (the vuvosun, futepel and nipapel shapes: "
+                                                                      "nipapel-w1024", "nipapel-w2048", "sebalorn-w1024", "sebalorn-w2048"],
+                   help="a named shape; the default is the benchmark's (the vuvosun, futepel, nipapel and sebalorn shapes: "
                         "with --profile-case only; their numbers come from --compare)")
     p.add_argument("--layers", type=int, default=0,
                    help="fewer layers than the shape has (both numbers are reported)")
     p.add_argument("--profile-case", default=None, choices=["prefill", "decode"],
                    help="run a small eager workload for a profiler instead of the benchmark")
-    p.add_argument("--compare", default=None, choices=["vuvosun", "futepel", "nipapel"],
+    p.add_argument("--compare", default=None, choices=["vuvosun", "futepel", "nipapel", "sebalorn"],
                    help="instead of the benchmark: this design beside the dense decoder at equal sizes")
     args = p.parse_args()
     if args.compare:

@@ -129,3 +129,34 @@ def nipapel(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab
 
 SHAPES["nipapel-w1024"] = nipapel(*COMPARISON_SIZES["w1024"])
 SHAPES["nipapel-w2048"] = nipapel(*COMPARISON_SIZES["w2048"])
+
+
+def sebalorn(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, vocab: int,
+             layers: int = 4, passes: int = 1) -> dict:
+    """A Sebalorn config.json of a real model's proportions: `layers` layers that take turns as
+    attention (q and k normed over the whole projection, a gate per head) + dense feed-forward,
+    retention + dense, latent attention with a sink + dense, attention + dense; every mixer
+    `heads * head_dim` wide, the latent's cached row 256 features (192 of latent, 64 rotated),
+    the queries' latent half the model's width.  Layers 1 and 2 form the repeated run, `passes`
+    times (1: every layer runs once, so the model does the work of `layers` layers)."""
+    dense = {"kind": "dense", "ff": ff}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                 "scale": head_dim ** -0.5, "rot": {"base": 10000.0, "dims": head_dim // 2}}
+    retention = {"heads": heads, "dim": head_dim, "vdim": head_dim,
+                 "decay": [1.0 - 2.0 ** (-5 - 0.5 * (i % 8)) for i in range(heads)],
+                 "rot": {"base": 10000.0, "dims": head_dim}}
+    latent = {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 192,
+              "q_rank": width // 2, "scale": (head_dim + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    cycle = [("attention", attention), ("retention", retention), ("latent_attention", latent),
+             ("attention", attention)]
+    out = {"architecture": "Sebalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+           "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0,
+           "layers": [{"type": cycle[i % 4][0], "mixer": dict(cycle[i % 4][1]), "mlp": dense}
+                      for i in range(layers)]}
+    if layers >= 3:
+        out["loop"] = {"start": 1, "stop": 3, "times": passes}
+    return out
+
+
+SHAPES["sebalorn-w1024"] = sebalorn(*COMPARISON_SIZES["w1024"])
+SHAPES["sebalorn-w2048"] = sebalorn(*COMPARISON_SIZES["w2048"])

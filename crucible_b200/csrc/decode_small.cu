@@ -13,7 +13,8 @@
 //             normalised rows never go to global memory;
 //   epilogues ACCUM_F32    out[m, n] += dot               (output projections)
 //             STORE_F32    out[m, n]  = dot               (logits)
-//             STORE_BF16   out[m, n]  = bf16(dot)         (joint input projections)
+//             STORE_BF16   out[m, n]  = bf16(dot)         (joint input projections), or
+//                          bf16(max(dot, 0)^2) with `act` 1 (a feed-forward's first product)
 //             SWIGLU_BF16  out[m, i]  = silu(g_i) * u_i   (gate and up rows paired)
 //             ROPE_APPEND  rows (j, j + hd/2) of a head paired: q rotated and
 //                          stored, k rotated into the request's cache page,
@@ -67,6 +68,7 @@ struct SmallParams {
     __nv_bfloat16* v_cache;
     int n_heads, n_kv_heads, head_dim, page_tokens, write_cache;
     float glu_limit, glu_alpha, glu_offset;   // SWIGLU: limit > 0: the capped pair instead of silu(g) * u
+    int act;                      // STORE_BF16: 1: max(dot, 0)^2 instead of the dot
     int trigger_early;            // let the kernel after this one start as soon as this one's weights are asked for
                                   // (the q/k/v product: measured on B200 at batch 1 / 8, 2,048-token contexts,
                                   // 0.291 -> 0.286 / 0.345 -> 0.330 ms per step; for the other products 0 to
@@ -370,8 +372,10 @@ __global__ void __launch_bounds__(WARPS * 32) small_linear_kernel(const SmallPar
             const float df = d[e], ds = d[2 + e];
             if (EPI == STORE_BF16) {
                 __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)m * p.ldc;
-                if (ok_f) out[rf] = __float2bfloat16_rn(df);
-                if (ok_s) out[rs] = __float2bfloat16_rn(ds);
+                const float af = p.act == 1 ? fmaxf(df, 0.f) * fmaxf(df, 0.f) : df;
+                const float as = p.act == 1 ? fmaxf(ds, 0.f) * fmaxf(ds, 0.f) : ds;
+                if (ok_f) out[rf] = __float2bfloat16_rn(af);
+                if (ok_s) out[rs] = __float2bfloat16_rn(as);
             } else if (EPI == ACCUM_F32 || EPI == STORE_F32) {
                 float* out = (float*)p.out + (size_t)m * p.ldc;
                 if (ok_f) out[rf] = EPI == ACCUM_F32 ? old[nt][e] + df : df;
@@ -476,13 +480,13 @@ CB_EXPORT int cb_small_linear(const float* x, const float* gain, float eps, cons
 // out[M, N] (bf16) = act W^T.
 CB_EXPORT int cb_small_linear_bf16(const float* x, const float* gain, float eps, const void* a, int lda,
                                    const void* w, int ldw, void* out, int ldc, int M, int N, int K,
-                                   void* stream) {
+                                   int act, void* stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (!sizes_ok(x, gain, a, lda, M, K, ldw, w)) return CB_ERR_UNSUPPORTED;
+    if (!sizes_ok(x, gain, a, lda, M, K, ldw, w) || act < 0 || act > 1) return CB_ERR_UNSUPPORTED;
     SmallParams p = {};
     p.x = x; p.gain = gain; p.eps = eps; p.a = (const __nv_bfloat16*)a; p.lda = lda;
     p.w = (const __nv_bfloat16*)w; p.ldw = ldw; p.M = M; p.K = K; p.N = N;
-    p.n_tiles = (N + 15) / 16; p.out = out; p.ldc = ldc;
+    p.n_tiles = (N + 15) / 16; p.out = out; p.ldc = ldc; p.act = act;
     cudaStream_t s = (cudaStream_t)stream;
     return x ? launch_rows<true, STORE_BF16>(p, s) : launch_rows<false, STORE_BF16>(p, s);
 }

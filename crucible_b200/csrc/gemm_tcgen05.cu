@@ -6,7 +6,7 @@
 // and issues the MMAs, warps 2-5 do the epilogue.  One output tile per block.
 //
 // Epilogues (fused where it saves memory traffic):
-//   STORE_BF16  C bf16 = acc
+//   STORE_BF16  C bf16 = acc, or act(acc) with NormArgs::act (1: the square of relu)
 //   STORE_F32   C fp32 = acc                      (logits)
 //   ACCUM_F32   C fp32 += acc                     (residual add in 32 bits)
 //   SWIGLU_BF16 W = [Wg; Wu] ([2I, K]); the tile holds BN/2 gate rows and the
@@ -95,6 +95,8 @@ struct NormArgs {
     // W and whose results go to columns z * head_c_cols + [0, N) of C.  K is a head's K; what a
     // block of 64 columns of A holds beyond it meets columns of W outside its map, which read zero.
     int heads, head_a_cols, head_c_cols;
+    // STORE_BF16: an activation on the way out; 0: none, 1: max(x, 0)^2
+    int act;
 };
 
 template <int BN, int STAGES, int MH>
@@ -669,6 +671,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
                                     for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * f);
                                 }
+                                if (EPI == STORE_BF16 && na.act == 1) {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j) {
+                                        const float z = fmaxf(__uint_as_float(v[j]), 0.f);
+                                        v[j] = __float_as_uint(z * z);
+                                    }
+                                }
                             }
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
@@ -778,6 +787,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     if (PRE) {
 #pragma unroll
                         for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * rf[0]);
+                    }
+                    if (EPI == STORE_BF16 && na.act == 1) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float z = fmaxf(__uint_as_float(r[j]), 0.f);
+                            r[j] = __float_as_uint(z * z);
+                        }
                     }
                     const bool full = col0 + 32 <= N;
                     if (EPI == STORE_BF16) {

@@ -82,17 +82,31 @@ __global__ void latent_prepare_kernel(const T* __restrict__ dkv, int dkv_stride,
     }
 }
 
-// x[t][h][:] *= sigmoid(logit[t][h])
-template <typename T>
-__global__ void head_gate_kernel(T* __restrict__ x, int x_stride, const float* __restrict__ logit,
+// x[t][h][:] *= sigmoid(logit[t][h]); the logits are float32 or rows of T (columns of a joint
+// projection).  Eight values of T a thread where the rows allow it.
+template <typename T, typename L>
+__global__ void head_gate_kernel(T* __restrict__ x, int x_stride, const L* __restrict__ logit,
                                  int logit_stride, int n_rows, int n_heads, int E) {
     cb_pdl_trigger();
     cb_pdl_wait();
     const int t = blockIdx.x;
+    T* xr = x + (size_t)t * x_stride;
+    const L* lr = logit + (size_t)t * logit_stride;
+    constexpr int VEC = 16 / sizeof(T);
+    if (E % VEC == 0 && x_stride % VEC == 0 && ((uintptr_t)x & 15) == 0) {
+        for (int i = threadIdx.x * VEC; i < n_heads * E; i += blockDim.x * VEC) {
+            const float g = 1.0f / (1.0f + expf(-cb_to_float(lr[i / E])));
+            uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
+            T* v = reinterpret_cast<T*>(&raw);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) v[j] = cb_from_float<T>(cb_to_float(v[j]) * g);
+            *reinterpret_cast<uint4*>(xr + i) = raw;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n_heads * E; i += blockDim.x) {
-        const float g = 1.0f / (1.0f + expf(-logit[(size_t)t * logit_stride + i / E]));
-        T* at = x + (size_t)t * x_stride + i;
-        *at = cb_from_float<T>(cb_to_float(*at) * g);
+        const float g = 1.0f / (1.0f + expf(-cb_to_float(lr[i / E])));
+        xr[i] = cb_from_float<T>(cb_to_float(xr[i]) * g);
     }
 }
 
@@ -229,16 +243,21 @@ CB_EXPORT int cb_rows_gate(void* x, int x_stride, const void* g, int g_stride, i
     return cb_last_error();
 }
 
-CB_EXPORT int cb_head_gate(void* x, int x_stride, int dtype, const float* logit, int logit_stride,
-                           int n_rows, int n_heads, int E, void* stream) {
+// logit_dtype: float32 logits, or logits of the rows' own dtype.
+CB_EXPORT int cb_head_gate(void* x, int x_stride, int dtype, const void* logit, int logit_dtype,
+                           int logit_stride, int n_rows, int n_heads, int E, void* stream) {
     if (n_rows <= 0) return 0;
-    const dim3 grid(n_rows), block(n_heads * E >= 1024 ? 256 : 128);
+    if (logit_dtype != CB_F32 && logit_dtype != dtype) return CB_ERR_UNSUPPORTED;
+    const dim3 grid(n_rows), block(n_heads * E >= 2048 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == CB_F32)
-        cb_launch(head_gate_kernel<float>, grid, block, 0, s, (float*)x, x_stride, logit, logit_stride,
-                  n_rows, n_heads, E);
-    else
-        cb_launch(head_gate_kernel<__nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)x, x_stride, logit,
+        cb_launch(head_gate_kernel<float, float>, grid, block, 0, s, (float*)x, x_stride, (const float*)logit,
                   logit_stride, n_rows, n_heads, E);
+    else if (logit_dtype == CB_F32)
+        cb_launch(head_gate_kernel<__nv_bfloat16, float>, grid, block, 0, s, (__nv_bfloat16*)x, x_stride,
+                  (const float*)logit, logit_stride, n_rows, n_heads, E);
+    else
+        cb_launch(head_gate_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, s, (__nv_bfloat16*)x,
+                  x_stride, (const __nv_bfloat16*)logit, logit_stride, n_rows, n_heads, E);
     return cb_last_error();
 }

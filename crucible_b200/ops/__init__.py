@@ -341,6 +341,26 @@ def linear(a, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False, c
     linear_plain(a, w, out, accumulate=accumulate)
 
 
+FUSED_ACTIVATIONS = {"relu2": 1}     # activations the bfloat16 products apply on their results' way out
+FUSE_ACTIVATION = True               # tests switch it off to reach the product and the pass after it
+
+
+def linear_act(h, w: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(h W^T): for a bfloat16 weight and an activation of `FUSED_ACTIVATIONS` one
+    kernel (the activation in the product's epilogue, on the float32 sums, rounded once); else the
+    product and then `activation` in place."""
+    from . import small_batch
+    code = FUSED_ACTIVATIONS.get(kind, 0)
+    if FUSE_ACTIVATION and code and w.dtype == torch.bfloat16 and is_weight(w) and out.dtype == torch.bfloat16:
+        if h.shape[0] <= small_batch.PREFERRED_ROWS and small_batch.linear(h, w, out, act=code):
+            return
+        from . import tensor_core
+        if tensor_core.linear(small_batch.as_tensor(h), w, out, act=code):
+            return
+    linear(h, w, out)
+    activation(kind, out, out)
+
+
 def _norm_emit(ctx, rows: torch.Tensor, tensor_core):
     """What the accumulate product into `rows` may leave for the norm announced for them."""
     ahead = getattr(ctx, "norm_ahead", None)

@@ -40,14 +40,16 @@ def prepare(dkv, q, qx, gain, freq, mscale: float, eps: float, n_heads: int, dim
 
 
 def head_gate(x, logit, n_heads: int, head_width: int) -> None:
-    """x[t, h, :] *= sigmoid(logit[t, h]) in place; `logit` float32 [rows, heads]."""
+    """x[t, h, :] *= sigmoid(logit[t, h]) in place; `logit` [rows, heads] in float32 or in the
+    rows' own dtype (columns of a joint projection)."""
     _need_cuda(x, logit)
-    if logit.dtype != torch.float32 or logit.stride(1) != 1 or x.stride(1) != 1 or x.shape[1] != n_heads * head_width:
-        raise KernelError("head_gate: rows [T, heads * width] and float32 logits [T, heads]")
+    if (logit.dtype not in (torch.float32, x.dtype) or logit.stride(1) != 1 or x.stride(1) != 1
+            or x.shape[1] != n_heads * head_width or logit.shape[1] != n_heads):
+        raise KernelError("head_gate: rows [T, heads * width] and logits [T, heads], float32 or the rows' dtype")
     lib = build.load("latent_attention")
     _check(lib.cb_head_gate(_ptr(x), _c_int(x.stride(0)), _c_int(_code(x.dtype)), _ptr(logit),
-                            _c_int(logit.stride(0)), _c_int(x.shape[0]), _c_int(n_heads),
-                            _c_int(head_width), _stream()), "head_gate")
+                            _c_int(_code(logit.dtype)), _c_int(logit.stride(0)), _c_int(x.shape[0]),
+                            _c_int(n_heads), _c_int(head_width), _stream()), "head_gate")
 
 
 def rows_gate(x, g) -> None:

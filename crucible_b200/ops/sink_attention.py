@@ -124,9 +124,13 @@ def _tensor_cores(q, gate, out, sinks, n_heads, n_kv_heads, key_dim, value_dim, 
     from . import tensor_core
     # a plain softmax over keys and values of 64 or 128 features, portions of prompts only: the
     # tcgen05 attention, whose tiles take the kept first tokens ahead of the window's
-    if (sinks is None and gate is None and out_scale == 1.0
+    if (sinks is None and (gate is None or gate_per_head) and out_scale == 1.0
             and tensor_core.prompt_attention(q, out, k_cache, v_cache, n_heads, n_kv_heads, key_dim, scale,
                                              window, keep_first, ctx, cache, table)):
+        if gate is not None:
+            # one logit a head: a pass over the heads' results behind the attention
+            from . import latent
+            latent.head_gate(out, gate, n_heads, value_dim)
         return True
     lib = build.load("attention_mma")
     # Few rows per request (decoded tokens, short portions): one row tile each, so the blocks

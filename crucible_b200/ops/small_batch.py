@@ -113,10 +113,11 @@ def _weights_ok(w: torch.Tensor, rows: int) -> bool:
 MAX_OUT_ROWS = 8192     # wider products (the LM head) stream better through the tensor-core kernel
 
 
-def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False) -> bool:
+def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = False, act: int = 0) -> bool:
+    """`act` 1 (a bfloat16 result only): the square of relu of every dot product."""
     if (not _weights_ok(w, h.shape[0]) or out.stride(1) != 1 or w.shape[0] > MAX_OUT_ROWS
             or out.dtype not in (torch.float32, torch.bfloat16)
-            or (accumulate and out.dtype != torch.float32)):
+            or (accumulate and out.dtype != torch.float32) or (act and out.dtype != torch.bfloat16)):
         return False
     inp = _input(h, w)
     if inp is None:
@@ -127,7 +128,7 @@ def linear(h: Rows, w: torch.Tensor, out: torch.Tensor, *, accumulate: bool = Fa
         return _done(lib.cb_small_linear_bf16(_ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda),
                                               _ptr(w), _c_int(w.stride(0)), _ptr(out),
                                               _c_int(out.stride(0)), _c_int(h.shape[0]),
-                                              _c_int(w.shape[0]), _c_int(w.shape[1]), _stream()),
+                                              _c_int(w.shape[0]), _c_int(w.shape[1]), _c_int(act), _stream()),
                      "small linear (bf16 result)")
     return _done(lib.cb_small_linear(_ptr(x), _ptr(gain), _c_float(eps), _ptr(a), _c_int(lda),
                                      _ptr(w), _c_int(w.stride(0)), _ptr(out), _c_int(out.stride(0)),

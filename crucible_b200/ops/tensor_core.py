@@ -182,7 +182,7 @@ class _NormArgs(ctypes.Structure):
                 ("glu_limit", ctypes.c_float), ("glu_alpha", ctypes.c_float), ("glu_offset", ctypes.c_float),
                 ("plan", ctypes.c_void_p), ("n_experts", ctypes.c_int), ("max_tiles", ctypes.c_int),
                 ("w_rows", ctypes.c_int), ("heads", ctypes.c_int), ("head_a_cols", ctypes.c_int),
-                ("head_c_cols", ctypes.c_int)]
+                ("head_c_cols", ctypes.c_int), ("act", ctypes.c_int)]
 
 
 class NormEmit:
@@ -197,12 +197,14 @@ class NormEmit:
         self.parts = None
 
 
-def _norm_args(emit, pre, rows: int, pair=None):
+def _norm_args(emit, pre, rows: int, pair=None, act: int = 0):
     """The pointer the product kernels take, and the object that keeps it alive.  `pair`:
-    (limit, alpha, offset) of the capped gated pair for the SwiGLU form."""
-    if emit is None and pre is None and pair is None:
+    (limit, alpha, offset) of the capped gated pair for the SwiGLU form.  `act`: an activation
+    on a bfloat16 result's way out (1: the square of relu)."""
+    if emit is None and pre is None and pair is None and not act:
         return _c_void_p(0), None
     args = _NormArgs()
+    args.act = int(act)
     if pair is not None:
         args.glu_limit, args.glu_alpha, args.glu_offset = (float(v) for v in pair)
     if emit is not None:
@@ -216,11 +218,11 @@ def _norm_args(emit, pre, rows: int, pair=None):
     return ctypes.cast(ctypes.pointer(args), _c_void_p), args
 
 
-def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None, pair=None) -> bool:
+def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None, pair=None, act=0) -> bool:
     lib = build.load("gemm_tcgen05")
     if per_sm == 0:
         # 256 x 256 tiles; an output that cannot leave by TMA is refused, and the 128-row tiles run
-        if _gemm(a, w, out, n, epi, 256, -1, 1, None, pre, pair):
+        if _gemm(a, w, out, n, epi, 256, -1, 1, None, pre, pair, act):
             return True
         per_sm = 1
     if per_sm == -1:
@@ -230,7 +232,7 @@ def _gemm(a, w, out, n, epi, bn, per_sm=1, splits=None, emit=None, pre=None, pai
     if emit is not None and (epi != ACCUM_F32 or bn > NORM_AHEAD_MAX_TILE or per_sm == 0 or n % 32
                              or emit.sumsq.shape[0] < -(-n // bn) or emit.sumsq.stride(0) != a.shape[0]):
         emit = None
-    norm_ptr, keep = _norm_args(emit, pre, a.shape[0], pair)
+    norm_ptr, keep = _norm_args(emit, pre, a.shape[0], pair, act)
     code = lib.cb_gemm_tcgen05(
         _c_void_p(a.data_ptr()), _c_void_p(w.data_ptr()), _c_void_p(out.data_ptr()),
         _c_int(a.shape[0]), _c_int(n), _c_int(a.shape[1]), _c_int(a.stride(0)),
@@ -321,11 +323,14 @@ def _operands_ok(a, w) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def linear(a, w, out, *, accumulate=False, tile=None, emit=None, pre=None) -> bool:
+def linear(a, w, out, *, accumulate=False, tile=None, emit=None, pre=None, act=0) -> bool:
     """`emit` (`NormEmit`): with accumulate, also leave the next norm's input if this product's
     form can (`emit.parts` says whether it did).  `pre` (`small_batch.LazyNorm` with `scaled`):
-    `a` is that norm input, the rows' factors are applied in the epilogue."""
+    `a` is that norm input, the rows' factors are applied in the epilogue.  `act` 1 (a bfloat16
+    result through the 128-row tiles): the square of relu in the epilogue."""
     if not _operands_ok(a, w) or out.stride(1) != 1:
+        return False
+    if act and out.dtype != torch.bfloat16:
         return False
     if out.dtype == torch.bfloat16:
         if accumulate:
@@ -339,13 +344,13 @@ def linear(a, w, out, *, accumulate=False, tile=None, emit=None, pre=None) -> bo
     if tile is None and ((a.shape[0] <= SKINNY_ROWS and w_bytes >= SKINNY_MIN_BYTES)
                          or (a.shape[0] <= SKINNY_MID_ROWS and SKINNY_MIN_BYTES <= w_bytes <= SKINNY_MID_BYTES)
                          or (a.shape[0] <= 64 and w.shape[0] >= SKINNY_WIDE_N)):
-        if pre is not None:
+        if pre is not None or act:
             return False
         return _gemm_skinny(a, w, out, w.shape[0], epi)
     if tile is None and _tall_tiles(a.shape[0], w.shape[0], a.shape[1]):
         tile = (256, 0)
     bn, per_sm, *splits = _tile_of(tile) if tile else _tile_width(a.shape[0], w.shape[0], epi)
-    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None, emit, pre)
+    return _gemm(a, w, out, w.shape[0], epi, bn, per_sm, splits[0] if splits else None, emit, pre, None, act)
 
 
 def grouped_linear(a, w, out, plan, n_experts: int, tiles: int, gated: bool, pair=None) -> bool:

@@ -48,8 +48,7 @@ class ActivatedFeedForward(FeedForward):
 
     def forward(self, ctx, h, residual):
         z = ctx.scratch("ffn.z", (h.shape[0], self.spec.intermediate), self.dtype)
-        ops.linear(h, self.up, z)
-        ops.activation(self.kind, z, z)
+        ops.linear_act(h, self.up, z, self.kind)
         ops.linear(z, self.down, residual, accumulate=True, closes=ctx)
 
 

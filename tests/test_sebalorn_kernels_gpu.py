@@ -286,3 +286,30 @@ def test_retention_remembers_the_first_token_with_a_decay_of_one():
             state = decay * state + k[i][:, None] * v[i][None, :]
         out = state.T @ k[0]
         assert torch.allclose(out, v[0] * decay ** (T - 1))
+
+
+# ---------------------------------------------------------------------------
+# the dense feed-forward: the square of relu on the first product's way out
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,ff,rows", [(40, 72, 19), (128, 256, 150), (44, 52, 1), (64, 96, 8), (256, 704, 300)])
+def test_dense_feed_forward_with_the_square_of_relu(dtype, width, ff, rows, monkeypatch):
+    from crucible_b200 import ops
+    from crucible_b200.config.model_config import FeedForwardSpec
+    from crucible_b200.parts import FEED_FORWARDS
+    part = FEED_FORWARDS.build("dense_act", FeedForwardSpec(kind="dense_act", width=width, intermediate=ff,
+                                                            extra=(("activation", "relu2"),)))
+    w = _bind(part, dtype, 3, std=0.2)
+    h = torch.randn(rows, width).to(torch.bfloat16).float()
+    ref = plain.dense_feed_forward(h.double(), w, "")
+    results = []
+    for fused in (True, False):
+        monkeypatch.setattr(ops, "FUSE_ACTIVATION", fused)
+        res = torch.zeros(rows, width, device=DEV)
+        part.forward(Steps(dtype).ctx([(0, rows)], None), h.to(dtype).to(DEV), res)
+        assert rel(res, ref) < TOL[dtype], fused
+        results.append(res.clone())
+    if dtype == torch.bfloat16:
+        # the two forms differ by one rounding of the first product, no more
+        assert rel(results[0], results[1]) < 1e-2
