@@ -79,6 +79,11 @@ class SinkWindowAttention(BranchMixer):
 
     def bind(self, tensors, dtype, device):
         parts = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.has_gate else [])
+        # rows of zeros behind a gate of a few logits, so that a row of the joint projection is a
+        # multiple of 16 bytes long (the tensor-core attention reads q in 16-byte pieces)
+        spare = -sum(t.shape[0] for t in parts) % 8
+        if spare and self.gate == "head":
+            parts.append(torch.zeros((spare, parts[0].shape[1]), dtype=parts[0].dtype, device=parts[0].device))
         self.w_in = torch.cat(parts, dim=0).contiguous()
         self.w_out = tensors["o"]
         self.sinks = tensors.get("sink") if self.has_sink else None
