@@ -143,14 +143,14 @@ def sebalorn(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, voca
     attention = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
                  "scale": head_dim ** -0.5, "rot": {"base": 10000.0, "dims": head_dim // 2}}
     retention = {"heads": heads, "dim": head_dim, "vdim": head_dim,
-                 "decay": [1.0 - 2.0 ** (-5 - 0.5 * (i % 8)) for i in range(heads)],
+                 "decay": [1.0 - 2.0 ** (-4 - 0.75 * (i % 8)) for i in range(heads)],
                  "rot": {"base": 10000.0, "dims": head_dim}}
     latent = {"heads": heads, "dim": head_dim, "rot_dim": 64, "vdim": head_dim, "kv_rank": 192,
               "q_rank": width // 2, "scale": (head_dim + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
     cycle = [("attention", attention), ("retention", retention), ("latent_attention", latent),
              ("attention", attention)]
     out = {"architecture": "Sebalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
-           "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0,
+           "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 50.0,
            "layers": [{"type": cycle[i % 4][0], "mixer": dict(cycle[i % 4][1]), "mlp": dense}
                       for i in range(layers)]}
     if layers >= 3:
