@@ -149,8 +149,11 @@ def _run_order(raw, n_layers: int):
         raise ConfigError(f"{where}: must be an object")
     start, stop = _count(loop, "start", where), _count(loop, "stop", where)
     times = KeyReader(loop, where).integer("times")
-    if not start < stop <= n_layers:
-        raise ConfigError(f"{where}: 'start' < 'stop' <= the number of layers, got {start} and {stop}")
+    if not start <= stop <= n_layers:
+        raise ConfigError(f"{where}: 'start' <= 'stop' <= the number of layers, got {start} and {stop}")
+    if start == stop:
+        # an empty run: nothing repeats and no vector is ever added (the table is still the model's)
+        return tuple(RunEntry(layer=i) for i in range(n_layers)), times
     order = [RunEntry(layer=i) for i in range(start)]
     for t in range(times):
         order += [RunEntry(layer=i, copy=t, add=(LOOP_VECTORS, t) if i == start else None)

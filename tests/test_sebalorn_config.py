@@ -57,6 +57,12 @@ def test_a_model_without_a_repeated_run_and_without_a_cap():
     assert parse_config(_config("se-b")).head.option("softcap") is None
     latent = cfg.layers[2].mixer
     assert latent.option("rot_dim") == 0 and latent.position is None
+    # an empty run repeats nothing; its table of vectors is still one of the model's tensors
+    empty = _config()
+    empty["loop"].update(start=2, stop=2, times=3)
+    cfg = parse_config(empty)
+    assert [(e.layer, e.copy, e.add) for e in cfg.run_order] == [(i, 0, None) for i in range(5)]
+    assert cfg.vectors == (("loop_step", 3),)
 
 
 @pytest.mark.parametrize("edit,word", [
@@ -71,7 +77,7 @@ def test_a_model_without_a_repeated_run_and_without_a_cap():
     (lambda c: c["layers"][0]["mlp"].update(kind="moe"), "kind"),
     (lambda c: c["layers"][0]["mlp"].pop("ff"), "ff"),
     (lambda c: c["loop"].update(stop=9), "stop"),
-    (lambda c: c["loop"].update(start=4), "start"),
+    (lambda c: c["loop"].update(start=5), "start"),
     (lambda c: c["loop"].update(times=0), "times"),
     (lambda c: c.pop("norm"), "norm"),
     (lambda c: c.update(logit_softcap=-1.0), "logit_softcap"),
